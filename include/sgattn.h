@@ -1,0 +1,134 @@
+/*
+ * sgattn.h -- C ABI of libsgattn.so: super-gemma's attention / KV kernels on NVIDIA B200 (sm_100a).
+ *
+ * The library replaces, for the attention and KV kernels only, the dispatch surface that
+ * `sg-model` uses on `sg-gpu` (a Rust API; the reference has no C ABI of its own).  Kernels are
+ * addressed exactly as in the reference: by REGISTRY NAME, with a fixed BINDING ORDER, a raw POD
+ * PUSH-CONSTANT block and a WORKGROUP GRID; per-step lengths live in the 16-byte STEP BUFFER on
+ * the device so that a graph recorded once can be replayed every step.
+ * Paths in comments are relative to the reference repository.
+ *
+ * Threading contract (crates/sg-gpu/src/context.rs:84-85): one submitting thread per context.
+ * Every function returns an SGB_* code; sgb_last_error() gives the text of the last failure.
+ * There is no CPU fallback: without a usable CUDA device sgb_ctx_create() fails.
+ */
+#ifndef SGATTN_H
+#define SGATTN_H
+
+#include <stddef.h>
+#include <stdint.h>
+
+#ifdef __cplusplus
+extern "C" {
+#endif
+
+/* Error codes; the first six mirror `GpuError` (crates/sg-gpu/src/lib.rs:30-44). */
+enum {
+    SGB_OK = 0,
+    SGB_ERR_NO_DEVICE = 1,      /* GpuError::Library / NoDevice */
+    SGB_ERR_UNKNOWN_KERNEL = 2, /* GpuError::UnknownKernel */
+    SGB_ERR_VALIDATION = 3,     /* GpuError::Validation: binding count, sizes, alignment, page ids */
+    SGB_ERR_CUDA = 4,           /* GpuError::Vk / Pipeline: a CUDA runtime or driver call failed */
+    SGB_ERR_TIMEOUT = 5,        /* a bounded wait ran out (host sync, or a device-side wait) */
+    SGB_ERR_BOUNDS = 6,         /* a kernel recorded an out-of-range index in the status word */
+    SGB_ERR_STATE = 7           /* call not legal now (e.g. graph_end without graph_begin) */
+};
+
+typedef struct sgb_ctx sgb_ctx;
+typedef struct sgb_buffer sgb_buffer;
+typedef struct sgb_kernel sgb_kernel;
+typedef struct sgb_graph sgb_graph;
+typedef struct sgb_timer sgb_timer;
+
+/* Library version and the text of the calling thread's last error. */
+const char *sgb_version(void);
+const char *sgb_last_error(void);
+
+/* ---- context: GpuContext::new (crates/sg-gpu/src/context.rs:103) ------------------------------ */
+/* One CUDA device, one stream.  sgb_ctx_create makes its own stream; `stream` (a cudaStream_t, NULL =
+ * the legacy default stream) lets a host
+ * that already owns a stream (e.g. a PyTorch process doing NCCL on it) order its work with ours. */
+int sgb_ctx_create(int device, sgb_ctx **out);
+int sgb_ctx_create_on_stream(int device, void *stream, sgb_ctx **out);
+void sgb_ctx_destroy(sgb_ctx *ctx);
+int sgb_ctx_device(const sgb_ctx *ctx);
+void *sgb_ctx_stream(const sgb_ctx *ctx);
+int sgb_ctx_sm_count(const sgb_ctx *ctx);
+
+/* Completion: submit_and_wait (crates/sg-gpu/src/graph.rs:645-667), but with a FINITE wait.
+ * Also reads and clears the device status word, so device-side SGB_ERR_TIMEOUT / SGB_ERR_BOUNDS
+ * surface here.  timeout_ms = 0 means 30 s. */
+int sgb_sync(sgb_ctx *ctx, uint32_t timeout_ms);
+
+/* ---- buffers: Buffer<T> (crates/sg-gpu/src/buffer.rs:80,112-162,257-278) ---------------------- */
+/* Device memory; create() zero-fills as new_buffer does.  The reference maps unified memory into
+ * the host; here upload/download are explicit copies ordered on the context's stream.  The
+ * *_async forms return at once (give them pinned host memory); the plain forms wait. */
+int sgb_buffer_create(sgb_ctx *ctx, size_t bytes, sgb_buffer **out);
+int sgb_buffer_adopt(sgb_ctx *ctx, void *device_ptr, size_t bytes, sgb_buffer **out); /* not owned */
+int sgb_buffer_slice(sgb_buffer *parent, size_t offset, size_t bytes, sgb_buffer **out); /* Buffer::slice */
+void sgb_buffer_retain(sgb_buffer *buf);
+void sgb_buffer_release(sgb_buffer *buf);
+void *sgb_buffer_device_ptr(const sgb_buffer *buf);
+size_t sgb_buffer_bytes(const sgb_buffer *buf);
+int sgb_buffer_upload(sgb_buffer *buf, size_t offset, const void *host, size_t bytes);
+int sgb_buffer_download(sgb_buffer *buf, size_t offset, void *host, size_t bytes);
+int sgb_buffer_upload_async(sgb_buffer *buf, size_t offset, const void *host, size_t bytes);
+int sgb_buffer_download_async(sgb_buffer *buf, size_t offset, void *host, size_t bytes);
+int sgb_buffer_fill_zero(sgb_buffer *buf);
+int sgb_host_alloc(size_t bytes, void **out); /* pinned host memory for the async copies */
+void sgb_host_free(void *p);
+
+/* StepState::write_to (crates/sg-gpu/src/graph.rs:29-61): u32[4] = pos, kv_len_sliding,
+ * kv_len_global, q0.  Ordered on the stream, so it may be called between graph launches. */
+int sgb_step_write(sgb_buffer *step, uint32_t pos, uint32_t kv_len_sliding, uint32_t kv_len_global, uint32_t q0);
+
+/* ---- kernel registry: KERNELS / kernel_blob / load_kernel (crates/sg-gpu/src/kernel.rs:18-41,79) */
+typedef struct {
+    const char *name;
+    uint32_t workgroup[3]; /* threads per workgroup of the REFERENCE variant (informational) */
+    uint32_t bindings;     /* number of storage-buffer bindings, indices 0..bindings-1 */
+    uint32_t push_bytes;   /* size of the push-constant block, 0 = none */
+    const char *signature; /* binding order, push layout and grid meaning, as text */
+} sgb_kernel_info;
+
+int sgb_kernel_count(void);
+int sgb_kernel_info_at(int index, sgb_kernel_info *out);
+int sgb_kernel_get(sgb_ctx *ctx, const char *name, sgb_kernel **out); /* SGB_ERR_UNKNOWN_KERNEL on a miss */
+int sgb_kernel_describe(const sgb_kernel *k, sgb_kernel_info *out);
+
+/* ---- dispatch: GraphRecorder::dispatch (crates/sg-gpu/src/graph.rs:203-211) and -------------- */
+/* dispatch_blocking (crates/sg-gpu/src/exec.rs:12-23).  Bindings are (index, buffer view); the  */
+/* push block is raw bytes of exactly push_bytes; groups keeps the reference's grid meaning per  */
+/* kernel (see `signature`).  Work is ordered on the stream, which gives the compute->compute    */
+/* barrier the reference recorder inserts before every dispatch (graph.rs:269-273).              */
+typedef struct {
+    uint32_t index;
+    sgb_buffer *buffer;
+} sgb_binding;
+
+int sgb_dispatch(sgb_ctx *ctx, const sgb_kernel *k, const sgb_binding *bindings, uint32_t n_bindings, const void *push,
+                 size_t push_bytes, const uint32_t groups[3]);
+int sgb_dispatch_blocking(sgb_ctx *ctx, const sgb_kernel *k, const sgb_binding *bindings, uint32_t n_bindings,
+                          const void *push, size_t push_bytes, const uint32_t groups[3]);
+/* How many of this library's kernels have been launched through ctx (graph replays included). */
+uint64_t sgb_launch_count(const sgb_ctx *ctx);
+
+/* ---- record once, replay: record_graph / submit_blocking (crates/sg-gpu/src/graph.rs:523-528, */
+/* 640-642).  Between begin and end every sgb_dispatch / sgb_step_write-free call is captured    */
+/* into a CUDA graph instead of running; the graph keeps its buffers alive.                      */
+int sgb_graph_begin(sgb_ctx *ctx);
+int sgb_graph_end(sgb_ctx *ctx, sgb_graph **out);
+int sgb_graph_launch(sgb_ctx *ctx, sgb_graph *g); /* asynchronous; follow with sgb_sync */
+void sgb_graph_destroy(sgb_graph *g);
+
+/* ---- timers: GpuTimer (crates/sg-gpu/src/graph.rs:334-381,404-473) ---------------------------- */
+int sgb_timer_create(sgb_ctx *ctx, uint32_t n_stamps, sgb_timer **out);
+int sgb_timer_stamp(sgb_ctx *ctx, sgb_timer *t, uint32_t index); /* also legal while recording */
+int sgb_timer_read_ns(sgb_timer *t, uint64_t *out_ns, uint32_t n); /* ns since stamp 0; syncs the events */
+void sgb_timer_destroy(sgb_timer *t);
+
+#ifdef __cplusplus
+}
+#endif
+#endif /* SGATTN_H */

@@ -1,0 +1,415 @@
+// Flash-attention prefill on tcgen05 tensor cores, head_dim 128, GQA 2.
+//
+// Semantics: single-pass online-softmax flash attention as attn_prefill_global_flash_sp.wgsl:118-188
+// (m_new = max over visible s*scale, p = exp(s*scale - m), l += p in f32 BEFORE P = f16(p),
+// O = O*corr + P*V, out = O / l), with the banded mask of attn_prefill_sliding.wgsl:53-57 and the
+// ring + chunk key sources of attn_prefill_sliding_ring.wgsl:88-140 as variants.  The Q8_0 paged
+// entry dequantises to f16(scale*q) first (the value attn_prefill_global_flash_sp_q8.wgsl:104
+// builds), then runs the same kernel.  Output is f32.
+//
+// One CTA = 64 query tokens x the 2 query heads of one kv head = 128 rows of S and O, so both
+// heads share every K/V tile (GQA grouping).  Per 64-key tile:
+//   TMA (128B swizzle, no multicast) -> smem K, V        thread 0
+//   S[128x64]  = Q K^T   tcgen05.mma kind::f16, D in TMEM  thread 0, 8 instructions (K = 16 each)
+//   row softmax in registers: thread r owns TMEM lane r (tcgen05.ld 32x32b), base-2 exponent,
+//       running max raised only when it grows by > 2^8; masked tiles only at the band edges,
+//       tiles wholly outside [qpos+1-window, qpos] are never visited
+//   P -> smem as f16 in the K-major swizzled layout, fence.proxy.async
+//   O[128x128] += P V    tcgen05.mma, V as the MN-major B operand straight from its [key][dim] tile
+// Two CTAs fit per SM (112 KB smem, 256 TMEM columns each), so one CTA's softmax overlaps the
+// other's MMAs.  Every mbarrier wait is bounded; TMEM is always freed.
+#include "sgb_common.cuh"
+#include "sgb_kernels.h"
+
+namespace sgb {
+
+int run_kv_dequant_paged(const LaunchArgs& a, const BufView& scales, const BufView& quants, const BufView& table,
+                         const BufView& dst, const BufView& step, uint32_t row_len, uint32_t page);
+
+namespace {
+
+constexpr int HD = 128;
+constexpr int G = 2;
+constexpr int BLOCK_TOK = 64;   // query tokens per CTA
+constexpr int BLOCK_M = 128;    // rows = tokens x G
+constexpr int BLOCK_N = 64;     // keys per tile
+constexpr int FLASH_THREADS = 128;
+constexpr int KV_STAGES = 2;
+constexpr uint32_t HALF_TILE = 64 * 128;           // one [64 rows][128 B] box
+constexpr uint32_t Q_BYTES = 2 * 2 * HALF_TILE;    // 2 dim-halves x 128 rows
+constexpr uint32_t KV_TILE_BYTES = 2 * HALF_TILE;  // 2 dim-halves x 64 keys
+constexpr uint32_t TMEM_COLS = 256;
+constexpr uint32_t TMEM_S = 0;    // S: 64 f32 columns
+constexpr uint32_t TMEM_O = 64;   // O: 128 f32 columns
+constexpr float RESCALE_T = 8.0f;
+
+struct __align__(1024) FlashSmem {
+    uint8_t q[2][2 * HALF_TILE];             // [dim half][128 rows x 128 B]
+    uint8_t k[KV_STAGES][2][HALF_TILE];      // [stage][dim half][64 keys x 128 B]
+    uint8_t v[KV_STAGES][2][HALF_TILE];
+    uint8_t p[2 * HALF_TILE];                // [128 rows x 128 B] = 64 f16 keys per row
+    uint64_t full[KV_STAGES];
+    uint64_t q_bar;
+    uint64_t s_bar;
+    uint64_t pv_bar;
+    uint32_t tmem_base;
+};
+
+struct FlashParams {
+    const uint32_t* step;
+    float* out;
+    uint32_t* status;
+    uint32_t m_tokens;   // query tokens in the chunk
+    uint32_t n_kv;
+    uint32_t window;     // 0 = none
+    uint32_t ring;       // TWO_SRC: ring slots
+    float scale;
+};
+
+// One 64-key tile: where it comes from and which absolute positions its rows hold.
+struct Tile {
+    int src;        // 0 = history / linear, 1 = chunk
+    int row0;       // TMA row coordinate of key 0 of the tile
+    int64_t pos0;   // absolute position of key 0
+    int64_t lo, hi; // positions of this source that are real: [lo, hi]
+};
+
+template <bool TWO_SRC>
+__global__ void __launch_bounds__(FLASH_THREADS, 2) flash_prefill_kernel(const __grid_constant__ CUtensorMap tm_q,
+                                                                         const __grid_constant__ CUtensorMap tm_k0,
+                                                                         const __grid_constant__ CUtensorMap tm_v0,
+                                                                         const __grid_constant__ CUtensorMap tm_k1,
+                                                                         const __grid_constant__ CUtensorMap tm_v1,
+                                                                         const FlashParams prm)
+{
+    extern __shared__ uint8_t smem_raw[];
+    FlashSmem& sm = *reinterpret_cast<FlashSmem*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~uintptr_t(1023));
+
+    const int tid = threadIdx.x, warp = tid >> 5;
+    const int n_qtiles = gridDim.x;
+    const int qt = n_qtiles - 1 - (int)blockIdx.x;  // longest (latest) tiles first
+    const int kvh = blockIdx.y;
+    const uint32_t m0 = (uint32_t)qt * BLOCK_TOK;
+    const int64_t q0 = prm.step[STEP_Q0];
+    const uint32_t tok_in_tile = min((uint32_t)BLOCK_TOK, prm.m_tokens - m0);
+
+    // ---- which key tiles this CTA visits -------------------------------------------------------------
+    const int64_t first_qpos = q0 + m0, last_qpos = q0 + m0 + tok_in_tile - 1;
+    const int64_t band_lo = (prm.window != 0 && first_qpos + 1 > (int64_t)prm.window) ? first_qpos + 1 - prm.window : 0;
+    int n_hist, n_tiles;
+    int64_t hist_pos0 = 0, chunk_c0 = 0;
+    if (TWO_SRC) {
+        // history: positions [band_lo, q0) in the ring; chunk: positions [max(q0, band_lo), last_qpos]
+        const int64_t h_lo = band_lo, h_hi = q0;  // half-open
+        hist_pos0 = (h_lo / BLOCK_N) * BLOCK_N;
+        n_hist = h_hi > h_lo ? (int)((h_hi - 1) / BLOCK_N - h_lo / BLOCK_N + 1) : 0;
+        const int64_t c_lo = (band_lo > q0 ? band_lo - q0 : 0), c_hi = last_qpos - q0;  // inclusive chunk rows
+        chunk_c0 = (c_lo / BLOCK_N) * BLOCK_N;
+        n_tiles = n_hist + (int)(c_hi / BLOCK_N - c_lo / BLOCK_N + 1);
+    } else {
+        hist_pos0 = (band_lo / BLOCK_N) * BLOCK_N;
+        n_hist = (int)(last_qpos / BLOCK_N - band_lo / BLOCK_N + 1);
+        n_tiles = n_hist;
+    }
+    auto tile_at = [&](int it) {
+        Tile t;
+        if (it < n_hist) {
+            t.src = 0;
+            t.pos0 = hist_pos0 + (int64_t)it * BLOCK_N;
+            t.row0 = (int)(TWO_SRC ? t.pos0 % prm.ring : t.pos0);
+            t.lo = 0;
+            t.hi = TWO_SRC ? q0 - 1 : INT64_MAX;
+        } else {
+            t.src = 1;
+            const int64_t c = chunk_c0 + (int64_t)(it - n_hist) * BLOCK_N;
+            t.pos0 = q0 + c;
+            t.row0 = (int)c;
+            t.lo = q0;
+            t.hi = INT64_MAX;
+        }
+        return t;
+    };
+
+    // ---- set-up -----------------------------------------------------------------------------------------
+    if (tid == 0) {
+        for (int i = 0; i < KV_STAGES; i++) mbar_init(&sm.full[i], 1);
+        mbar_init(&sm.q_bar, 1);
+        mbar_init(&sm.s_bar, 1);
+        mbar_init(&sm.pv_bar, 1);
+        mbar_fence_init();
+        tma_prefetch_desc(&tm_q);
+        tma_prefetch_desc(&tm_k0);
+        tma_prefetch_desc(&tm_v0);
+    }
+    if (warp == 0) {
+        tmem_alloc(&sm.tmem_base, TMEM_COLS);
+        tmem_relinquish();
+    }
+    tc_fence_before_sync();
+    __syncthreads();
+    tc_fence_after_sync();
+    const uint32_t tmem = sm.tmem_base;
+
+    auto load_kv = [&](int it) {
+        const Tile t = tile_at(it);
+        const int st = it % KV_STAGES;
+        const CUtensorMap* mk = (TWO_SRC && t.src) ? &tm_k1 : &tm_k0;
+        const CUtensorMap* mv = (TWO_SRC && t.src) ? &tm_v1 : &tm_v0;
+        mbar_arrive_expect_tx(&sm.full[st], 2 * KV_TILE_BYTES);
+        tma_load_3d(sm.k[st][0], mk, &sm.full[st], 0, kvh, t.row0);
+        tma_load_3d(sm.k[st][1], mk, &sm.full[st], 64, kvh, t.row0);
+        tma_load_3d(sm.v[st][0], mv, &sm.full[st], 0, kvh, t.row0);
+        tma_load_3d(sm.v[st][1], mv, &sm.full[st], 64, kvh, t.row0);
+    };
+
+    if (tid == 0) {
+        mbar_arrive_expect_tx(&sm.q_bar, Q_BYTES);
+        tma_load_3d(sm.q[0], &tm_q, &sm.q_bar, 0, kvh * G, (int)m0);
+        tma_load_3d(sm.q[1], &tm_q, &sm.q_bar, 64, kvh * G, (int)m0);
+        load_kv(0);
+    }
+
+    // Row r of the tile <-> TMEM lane r <-> thread r: token m0 + r/2, query head kvh*2 + r%2.
+    const int r = tid;
+    const uint32_t tok = m0 + (uint32_t)(r >> 1);
+    const int64_t qpos = q0 + tok;
+    const int64_t row_lo = (prm.window != 0 && qpos + 1 > (int64_t)prm.window) ? qpos + 1 - prm.window : 0;
+    const float scale2 = prm.scale * 1.4426950408889634f;
+    const uint32_t lane_addr = tmem + ((uint32_t)(warp * 32) << 16);
+    constexpr uint32_t IDESC_QK = umma_idesc_f16(BLOCK_M, BLOCK_N, 0, 0);
+    constexpr uint32_t IDESC_PV = umma_idesc_f16(BLOCK_M, HD, 0, 1);
+
+    float m_run = NEG_SENTINEL, l_run = 0.0f;
+    bool failed = false;
+
+    for (int it = 0; it < n_tiles; ++it) {
+        const int st = it % KV_STAGES;
+        const Tile t = tile_at(it);
+
+        if (tid == 0) {
+            // The other stage was last read by PV of tile it-1, which has completed (pv_bar below).
+            if (it + 1 < n_tiles) load_kv(it + 1);
+            if (it == 0) mbar_wait(&sm.q_bar, 0, prm.status, 401, failed);
+            mbar_wait(&sm.full[st], (it / KV_STAGES) & 1, prm.status, 402, failed);
+            tc_fence_after_sync();
+#pragma unroll
+            for (int h = 0; h < 2; h++) {
+#pragma unroll
+                for (int j = 0; j < 4; j++) {
+                    const uint64_t da = umma_desc_sw128(smem_u32(sm.q[h]) + j * 32, 16, 1024);
+                    const uint64_t db = umma_desc_sw128(smem_u32(sm.k[st][h]) + j * 32, 16, 1024);
+                    umma_f16_ss(tmem + TMEM_S, da, db, IDESC_QK, (h | j) ? 1u : 0u);
+                }
+            }
+            umma_commit(&sm.s_bar);
+        }
+        mbar_wait(&sm.s_bar, it & 1, prm.status, 403, failed);
+        tc_fence_after_sync();
+
+        // ---- softmax on this thread's row -----------------------------------------------------------
+        uint32_t sv[64];
+        {
+            uint32_t a[32], b[32];
+            tmem_ld_32x32b_x32(lane_addr + TMEM_S, a);
+            tmem_ld_32x32b_x32(lane_addr + TMEM_S + 32, b);
+            tc_wait_ld();
+#pragma unroll
+            for (int j = 0; j < 32; j++) {
+                sv[j] = a[j];
+                sv[32 + j] = b[j];
+            }
+        }
+        // A tile needs per-element masks only where it crosses a band edge or a source boundary.
+        const bool tile_masked = t.pos0 + BLOCK_N - 1 > first_qpos || t.pos0 < (prm.window ? (last_qpos + 1 > (int64_t)prm.window ? last_qpos + 1 - prm.window : 0) : 0) ||
+                                 t.pos0 < t.lo || t.pos0 + BLOCK_N - 1 > t.hi;
+        float s2[64];
+        float mx = -INFINITY;
+        if (tile_masked) {
+            const int64_t hi = min(qpos, t.hi), lo = max(row_lo, t.lo);
+#pragma unroll
+            for (int j = 0; j < 64; j++) {
+                const int64_t pos = t.pos0 + j;
+                s2[j] = (pos >= lo && pos <= hi) ? __uint_as_float(sv[j]) * scale2 : -INFINITY;
+                mx = fmaxf(mx, s2[j]);
+            }
+        } else {
+#pragma unroll
+            for (int j = 0; j < 64; j++) {
+                s2[j] = __uint_as_float(sv[j]) * scale2;
+                mx = fmaxf(mx, s2[j]);
+            }
+        }
+        const bool grow = mx > m_run + RESCALE_T;
+        float corr = 1.0f;
+        if (grow) {
+            corr = ex2(m_run - mx);
+            m_run = mx;
+            l_run *= corr;
+        }
+        uint32_t pk[32];
+        float lsum = 0.0f;
+#pragma unroll
+        for (int j = 0; j < 32; j++) {
+            const float p0 = ex2(s2[2 * j] - m_run), p1 = ex2(s2[2 * j + 1] - m_run);
+            lsum += p0 + p1;
+            pk[j] = pack_half2(p0, p1);
+        }
+        l_run += lsum;
+        // P row r, 16-byte chunk c (keys 8c..8c+7) sits at chunk c ^ (r & 7) of its 128-byte row.
+        {
+            uint8_t* prow = sm.p + r * 128;
+#pragma unroll
+            for (int c = 0; c < 8; c++)
+                *reinterpret_cast<uint4*>(prow + ((c ^ (r & 7)) << 4)) = make_uint4(pk[4 * c], pk[4 * c + 1], pk[4 * c + 2], pk[4 * c + 3]);
+        }
+        // ---- rescale O where a row's max moved (O is only defined after the first PV) --------------
+        if (it > 0 && __any_sync(0xffffffffu, grow)) {
+#pragma unroll
+            for (int c = 0; c < 4; c++) {
+                uint32_t o[32];
+                tmem_ld_32x32b_x32(lane_addr + TMEM_O + 32 * c, o);
+                tc_wait_ld();
+#pragma unroll
+                for (int j = 0; j < 32; j++) o[j] = __float_as_uint(__uint_as_float(o[j]) * corr);
+                tmem_st_32x32b_x32(lane_addr + TMEM_O + 32 * c, o);
+            }
+            tc_wait_st();
+        }
+        fence_proxy_async_smem();
+        tc_fence_before_sync();
+        __syncthreads();
+
+        if (tid == 0) {
+            tc_fence_after_sync();
+#pragma unroll
+            for (int j = 0; j < 4; j++) {
+                const uint64_t da = umma_desc_sw128(smem_u32(sm.p) + j * 32, 16, 1024);
+                const uint64_t db = umma_desc_sw128(smem_u32(sm.v[st][0]) + j * 2048, HALF_TILE, 1024);
+                umma_f16_ss(tmem + TMEM_O, da, db, IDESC_PV, (it | j) ? 1u : 0u);
+            }
+            umma_commit(&sm.pv_bar);
+        }
+        mbar_wait(&sm.pv_bar, it & 1, prm.status, 404, failed);
+        tc_fence_after_sync();
+    }
+
+    // ---- epilogue: out = O / l.  The TMEM loads are warp-wide, so every thread takes part and only
+    // the stores are predicated (rows past the end of the chunk are not written). -------------------------
+    {
+        const bool live = (uint32_t)(r >> 1) < tok_in_tile;
+        const float inv_l = 1.0f / l_run;
+        float* orow = prm.out + ((size_t)(live ? tok : m0) * (prm.n_kv * G) + kvh * G + (r & 1)) * HD;
+#pragma unroll
+        for (int c = 0; c < 4; c++) {
+            uint32_t o[32];
+            tmem_ld_32x32b_x32(lane_addr + TMEM_O + 32 * c, o);
+            tc_wait_ld();
+            if (live) {
+#pragma unroll
+                for (int j = 0; j < 8; j++)
+                    *reinterpret_cast<float4*>(orow + 32 * c + 4 * j) =
+                        make_float4(__uint_as_float(o[4 * j]) * inv_l, __uint_as_float(o[4 * j + 1]) * inv_l,
+                                    __uint_as_float(o[4 * j + 2]) * inv_l, __uint_as_float(o[4 * j + 3]) * inv_l);
+            }
+        }
+    }
+    tc_fence_before_sync();
+    __syncthreads();
+    if (warp == 0) tmem_dealloc(tmem, TMEM_COLS);
+}
+
+struct PushScaleWindow {
+    float scale;
+    uint32_t window;
+};
+struct PushScalePage {
+    float scale;
+    uint32_t page;
+};
+
+int encode_qkv_map(const LaunchArgs& a, CUtensorMap* tm, const BufView& buf, uint64_t heads, uint32_t box_heads,
+                   uint32_t box_rows, const char* what)
+{
+    const uint64_t rows = buf.bytes / (heads * HD * 2);
+    if (rows == 0) return fail_validation(a, std::string(what) + ": buffer holds no complete row");
+    if (reinterpret_cast<uintptr_t>(buf.ptr) & 15) return fail_validation(a, std::string(what) + ": buffer must be 16-byte aligned");
+    const uint64_t dims[3] = {HD, heads, rows};
+    const uint64_t strides[2] = {HD * 2, heads * HD * 2};
+    const uint32_t box[3] = {64, box_heads, box_rows};
+    return encode_tensor_map(a, tm, 1, 3, buf.ptr, dims, strides, box, 3);
+}
+
+template <bool TWO_SRC>
+int run_flash(const LaunchArgs& a, const BufView& q, const BufView& k0, const BufView& v0, const BufView* k1, const BufView* v1,
+              const BufView& out, const BufView& step, uint32_t n_kv, uint32_t m_tokens, float scale, uint32_t window,
+              uint32_t ring)
+{
+    if (n_kv == 0 || m_tokens == 0) return fail_validation(a, "flash prefill: groups must be [kv heads, query tokens]");
+    const size_t n_q = (size_t)n_kv * G;
+    if (q.bytes < (size_t)m_tokens * n_q * HD * 2) return fail_validation(a, "flash prefill: q buffer too small");
+    if (out.bytes < (size_t)m_tokens * n_q * HD * 4) return fail_validation(a, "flash prefill: out buffer too small");
+    if (step.bytes < 16) return fail_validation(a, "flash prefill: the step buffer holds 4 x u32");
+    if (reinterpret_cast<uintptr_t>(out.ptr) & 15) return fail_validation(a, "flash prefill: out must be 16-byte aligned");
+    CUtensorMap tq, tk0, tv0, tk1, tv1;
+    if (int r = encode_qkv_map(a, &tq, BufView{q.ptr, (size_t)m_tokens * n_q * HD * 2}, n_q, G, BLOCK_TOK, "q")) return r;
+    if (int r = encode_qkv_map(a, &tk0, k0, n_kv, 1, BLOCK_N, "k")) return r;
+    if (int r = encode_qkv_map(a, &tv0, v0, n_kv, 1, BLOCK_N, "v")) return r;
+    if (TWO_SRC) {
+        if (k0.bytes < (size_t)ring * n_kv * HD * 2 || v0.bytes < (size_t)ring * n_kv * HD * 2)
+            return fail_validation(a, "flash prefill: ring buffers smaller than the ring");
+        if (k1->bytes < (size_t)m_tokens * n_kv * HD * 2 || v1->bytes < (size_t)m_tokens * n_kv * HD * 2)
+            return fail_validation(a, "flash prefill: chunk K/V hold fewer than M rows");
+        if (int r = encode_qkv_map(a, &tk1, *k1, n_kv, 1, BLOCK_N, "k_chunk")) return r;
+        if (int r = encode_qkv_map(a, &tv1, *v1, n_kv, 1, BLOCK_N, "v_chunk")) return r;
+    } else {
+        tk1 = tk0;
+        tv1 = tv0;
+    }
+    const size_t smem = sizeof(FlashSmem) + 1024;
+    static bool attr_set[2][64] = {};
+    if (a.device < 64 && !attr_set[TWO_SRC][a.device]) {
+        if (int r = check_cuda(a, cudaFuncSetAttribute(flash_prefill_kernel<TWO_SRC>, cudaFuncAttributeMaxDynamicSharedMemorySize,
+                                                       (int)smem),
+                               "cudaFuncSetAttribute(flash_prefill)"))
+            return r;
+        attr_set[TWO_SRC][a.device] = true;
+    }
+    FlashParams prm{(const uint32_t*)step.ptr, (float*)out.ptr, a.status, m_tokens, n_kv, window, ring, scale};
+    const dim3 grid((m_tokens + BLOCK_TOK - 1) / BLOCK_TOK, n_kv);
+    flash_prefill_kernel<TWO_SRC><<<grid, FLASH_THREADS, smem, a.stream>>>(tq, tk0, tv0, tk1, tv1, prm);
+    ++*a.launches;
+    return check_cuda(a, cudaGetLastError(), "attn_prefill_flash");
+}
+
+}  // namespace
+
+// attn_prefill_flash_f16_d128: q, k, v, out f32, step.  push {scale, window}.  grid [KV, M].
+int launch_prefill_flash_f16_d128(const LaunchArgs& a)
+{
+    const PushScaleWindow p = *(const PushScaleWindow*)a.push;
+    return run_flash<false>(a, a.b[0], a.b[1], a.b[2], nullptr, nullptr, a.b[3], a.b[4], a.groups[0], a.groups[1], p.scale,
+                            p.window, 0);
+}
+
+// attn_prefill_sliding_ring_flash_d128: q, k_ring, v_ring, k_chunk, v_chunk, out f32, step.  push {scale}.
+int launch_prefill_sliding_ring_flash_d128(const LaunchArgs& a)
+{
+    const float scale = *(const float*)a.push;
+    return run_flash<true>(a, a.b[0], a.b[1], a.b[2], &a.b[3], &a.b[4], a.b[5], a.b[6], a.groups[0], a.groups[1], scale, 1024,
+                           1024);
+}
+
+// attn_prefill_paged_q8kv_flash_d128: q, k_quants, k_scales, v_quants, v_scales, page_table,
+// k_lin, v_lin (f16 scratch, rows x KV x 128), out f32, step.  push {scale, page}.  grid [KV, M].
+int launch_prefill_paged_q8kv_flash_d128(const LaunchArgs& a)
+{
+    const PushScalePage p = *(const PushScalePage*)a.push;
+    const uint32_t n_kv = a.groups[0];
+    if (n_kv == 0 || p.page == 0) return fail_validation(a, "paged flash prefill: kv heads and page must be > 0");
+    const uint32_t row_len = n_kv * HD;
+    if (int r = run_kv_dequant_paged(a, a.b[2], a.b[1], a.b[5], a.b[6], a.b[9], row_len, p.page)) return r;
+    if (int r = run_kv_dequant_paged(a, a.b[4], a.b[3], a.b[5], a.b[7], a.b[9], row_len, p.page)) return r;
+    return run_flash<false>(a, a.b[0], a.b[6], a.b[7], nullptr, nullptr, a.b[8], a.b[9], n_kv, a.groups[1], p.scale, 0, 0);
+}
+
+}  // namespace sgb

@@ -1,0 +1,219 @@
+"""GPU parity for prefill attention through the C ABI: the reference-shaped scalar kernels replay
+the reference's seeded cases (crates/sg-gpu/tests/parity_attn.rs:252,342,435); the head_dim-128
+tcgen05 flash kernels (f16 linear, ring + chunk, paged Q8_0) are held to max-abs 2e-3 / relative
+1e-2 against the f64 oracle, and cross-checked against the scalar kernels on the same inputs."""
+import numpy as np
+import pytest
+
+from cases import D, G, H, KV, PAGE, SCALE, assert_close, bind, normal_f16, page_table, q8_pool
+from oracle import sg_oracle as O
+
+pytestmark = pytest.mark.gpu
+
+N_Q = 32
+
+
+@pytest.fixture(scope="module")
+def ctx():
+    import super_gemma_b200 as sg
+
+    return sg.GpuContext(0)
+
+
+def _step(ctx, **kw):
+    import super_gemma_b200 as sg
+
+    s = ctx.new_step_buffer()
+    sg.StepState(**kw).write_to(s)
+    return s
+
+
+# ---- reference-shaped scalar kernels ------------------------------------------------------------------
+@pytest.mark.parametrize("q0", [0, 1000])
+def test_attn_prefill_sliding_matches_reference(ctx, q0):  # parity_attn.rs:252
+    n_kv, hd, m, W = 16, 256, 64, 1024
+    rng = O.Rng(0xA7B + q0)
+    L = q0 + m
+    q = O.through_f16(rng.f32_vec(m * N_Q * hd))
+    k = O.through_f16(rng.f32_vec(L * n_kv * hd))
+    v = O.through_f16(rng.f32_vec(L * n_kv * hd))
+    b = lambda x: ctx.buffer_from_iter(O.f32_to_f16_bits(x))
+    out = ctx.new_buffer(m * N_Q * hd, np.uint16)
+    ctx.dispatch_blocking(ctx.load_kernel("attn_prefill_sliding"), bind(b(q), b(k), b(v), out, _step(ctx, q0=q0)), 0.0625,
+                          [n_kv, m, 1])
+    got = O.f16_bits_to_f32(out.read()).reshape(m, N_Q, hd)
+    heads = [0, 1, 9, 16, 31]
+    want = O.attention_f64(q.reshape(m, N_Q, hd), k.reshape(L, n_kv, hd), v.reshape(L, n_kv, hd), m, q0, N_Q, n_kv, hd, 0.0625,
+                           window=W, heads=heads)
+    assert_close(got[:, heads], want, 1e-2, 1e-2, f"prefill_sliding q0={q0}")
+
+
+def _ring_case(rng_vec, q0, m, n_kv, hd, R=1024):
+    row = n_kv * hd
+    L = q0 + m
+    q = O.through_f16(rng_vec(m * N_Q * hd)).reshape(m, N_Q, hd)
+    k_all = O.through_f16(rng_vec(L * row)).reshape(L, row)
+    v_all = O.through_f16(rng_vec(L * row)).reshape(L, row)
+    # history rows at slot pos % R in the pre-append ring; slots that hold nothing real keep junk
+    k_ring = O.through_f16(rng_vec(R * row)).reshape(R, row)
+    v_ring = O.through_f16(rng_vec(R * row)).reshape(R, row)
+    for t in range(max(0, q0 - R), q0):
+        k_ring[t % R] = k_all[t]
+        v_ring[t % R] = v_all[t]
+    return q, k_all, v_all, k_ring, v_ring
+
+
+@pytest.mark.parametrize("q0", [0, 100, 1000, 1531])
+def test_attn_prefill_sliding_ring_matches_reference(ctx, q0):  # parity_attn.rs:342
+    n_kv, hd, m = 16, 256, 64
+    rng = O.Rng(0xA7C + q0)
+    q, k_all, v_all, k_ring, v_ring = _ring_case(rng.f32_vec, q0, m, n_kv, hd)
+    b = lambda x: ctx.buffer_from_iter(O.f32_to_f16_bits(x))
+    out = ctx.new_buffer(m * N_Q * hd, np.uint16)
+    ctx.dispatch_blocking(ctx.load_kernel("attn_prefill_sliding_ring"),
+                          bind(b(q), b(k_ring), b(v_ring), b(k_all[q0:]), b(v_all[q0:]), out, _step(ctx, q0=q0)), 0.0625,
+                          [n_kv, m, 1])
+    got = O.f16_bits_to_f32(out.read()).reshape(m, N_Q, hd)
+    heads = [0, 1, 9, 16, 31]
+    L = q0 + m
+    want = O.attention_f64(q, k_all.reshape(L, n_kv, hd), v_all.reshape(L, n_kv, hd), m, q0, N_Q, n_kv, hd, 0.0625, window=1024,
+                           heads=heads)
+    assert_close(got[:, heads], want, 1e-2, 1e-2, f"prefill_sliding_ring q0={q0}")
+
+
+@pytest.mark.parametrize("q0", [0, 200])
+def test_attn_prefill_global_matches_reference(ctx, q0):  # parity_attn.rs:435
+    n_kv, hd, m = 4, 512, 64
+    rng = O.Rng(0xA7D + q0)
+    L = q0 + m
+    q = O.through_f16(rng.f32_vec(m * N_Q * hd))
+    k = O.through_f16(rng.f32_vec(L * n_kv * hd))
+    v = O.through_f16(rng.f32_vec(L * n_kv * hd))
+    b = lambda x: ctx.buffer_from_iter(O.f32_to_f16_bits(x))
+    out = ctx.new_buffer(m * N_Q * hd, np.uint16)
+    ctx.dispatch_blocking(ctx.load_kernel("attn_prefill_global"), bind(b(q), b(k), b(v), out, _step(ctx, q0=q0)), 0.044194174,
+                          [n_kv, m, 1])
+    got = O.f16_bits_to_f32(out.read()).reshape(m, N_Q, hd)
+    heads = [0, 7, 8, 31]
+    want = O.attention_f64(q.reshape(m, N_Q, hd), k.reshape(L, n_kv, hd), v.reshape(L, n_kv, hd), m, q0, N_Q, n_kv, hd,
+                           0.044194174, heads=heads)
+    assert_close(got[:, heads], want, 1e-2, 1e-2, f"prefill_global q0={q0}")
+
+
+# ---- head_dim 128: tcgen05 flash over linear f16 K/V ---------------------------------------------------
+def _linear_case(ctx, seed, m, q0, n_kv=KV):
+    L = q0 + m
+    q16, k16, v16 = normal_f16(seed, m, n_kv * G, D), normal_f16(seed + 1, L, n_kv, D), normal_f16(seed + 2, L, n_kv, D)
+    up = ctx.buffer_from_iter
+    return q16, k16, v16, [up(q16), up(k16), up(v16)]
+
+
+def _run_linear(ctx, kernel, bufs, m, q0, n_kv, push):
+    out = ctx.new_buffer(m * n_kv * G * D, np.float32)
+    ctx.dispatch_blocking(ctx.load_kernel(kernel), bind(*bufs, out, _step(ctx, q0=q0)), push, [n_kv, m, 1])
+    return out.read().reshape(m, n_kv * G, D)
+
+
+@pytest.mark.parametrize("m,q0,window", [(512, 0, 1024), (64, 0, 0), (100, 37, 0), (200, 1531, 1024), (256, 3000, 1024), (1, 5, 0),
+                                         (130, 900, 1024)])
+def test_flash_f16_linear(ctx, m, q0, window):
+    """(512, 0, 1024) is BASELINE config 1: 512 queries, f16 contiguous K/V, causal with a
+    1024-token window, f32 output."""
+    q16, k16, v16, bufs = _linear_case(ctx, 0x5601 + m + q0, m, q0)
+    want = O.attention_f64(q16.astype(np.float32), k16.astype(np.float32), v16.astype(np.float32), m, q0, H, KV, D, SCALE,
+                           window=window)
+    got = _run_linear(ctx, "attn_prefill_flash_f16_d128", bufs, m, q0, KV, (SCALE, window))
+    assert_close(got, want, what=f"flash f16 m={m} q0={q0} window={window}")
+    scalar = "attn_prefill_sliding_f32_d128" if window else "attn_prefill_global_f32_d128"
+    got_s = _run_linear(ctx, scalar, bufs, m, q0, KV, SCALE)
+    assert_close(got_s, want, what=f"scalar prefill m={m} q0={q0} window={window}")
+
+
+def test_flash_is_bit_deterministic(ctx):
+    q16, k16, v16, bufs = _linear_case(ctx, 0x5611, 192, 500)
+    a = _run_linear(ctx, "attn_prefill_flash_f16_d128", bufs, 192, 500, KV, (SCALE, 0))
+    b = _run_linear(ctx, "attn_prefill_flash_f16_d128", bufs, 192, 500, KV, (SCALE, 0))
+    assert np.array_equal(a.view(np.uint32), b.view(np.uint32))
+
+
+# ---- head_dim 128: ring history + chunk ------------------------------------------------------------------
+@pytest.mark.parametrize("q0,m", [(0, 64), (100, 64), (1000, 64), (1531, 64), (1531, 200), (66000, 4)])
+def test_sliding_ring_d128(ctx, q0, m):
+    """q0 = 1531 is the reference's wrapped-ring case; (66000, 4) is BASELINE config 4's sliding
+    part: a 4-token draft over a ring that has wrapped many times."""
+    R = 1024
+    rng = np.random.default_rng(0x5804 + q0 + m)
+    vec = lambda n: rng.standard_normal(n, dtype=np.float32)
+    # only the last R + m positions matter; shift positions so the arrays stay small
+    base = max(0, q0 - R)
+    q, k_all, v_all, k_ring, v_ring = _ring_case(vec, q0 - base, m, KV, D) if base == 0 else (None,) * 5
+    if base:
+        row = KV * D
+        L = R + m
+        q = O.through_f16(vec(m * H * D)).reshape(m, H, D)
+        k_all = O.through_f16(vec(L * row)).reshape(L, row)  # positions base .. q0 + m - 1
+        v_all = O.through_f16(vec(L * row)).reshape(L, row)
+        k_ring = np.empty((R, row), np.float32)
+        v_ring = np.empty((R, row), np.float32)
+        for t in range(base, q0):
+            k_ring[t % R] = k_all[t - base]
+            v_ring[t % R] = v_all[t - base]
+    hist = q0 - base
+    b = lambda x: ctx.buffer_from_iter(O.f32_to_f16_bits(x))
+    bufs = [b(q), b(k_ring), b(v_ring), b(k_all[hist:]), b(v_all[hist:])]
+    L = hist + m
+    want = O.attention_f64(q, k_all.reshape(L, KV, D), v_all.reshape(L, KV, D), m, hist, H, KV, D, SCALE, window=1024)
+    for kernel in ("attn_prefill_sliding_ring_f32_d128", "attn_prefill_sliding_ring_flash_d128", "attn_verify_sliding_ring_d128"):
+        out = ctx.new_buffer(m * H * D, np.float32)
+        ctx.dispatch_blocking(ctx.load_kernel(kernel), bind(*bufs, out, _step(ctx, q0=q0)), SCALE, [KV, m, 1])
+        assert_close(out.read().reshape(m, H, D), want, what=f"{kernel} q0={q0} m={m}")
+
+
+# ---- head_dim 128: paged Q8_0 K and V -----------------------------------------------------------------------
+def _paged_prefill(ctx, seed, m, q0, n_kv=KV, page=PAGE, identity=False):
+    L = q0 + m
+    n_pages = -(-L // page)
+    table = page_table(seed + 0x100, n_pages + 2, identity)[:n_pages]
+    q16 = normal_f16(seed, m, n_kv * G, D)
+    k = q8_pool(normal_f16(seed + 1, L, n_kv, D), table, page, n_pages + 2, seed + 2)
+    v = q8_pool(normal_f16(seed + 3, L, n_kv, D), table, page, n_pages + 2, seed + 4)
+    up = ctx.buffer_from_iter
+    bufs = [up(q16), up(k.quants), up(k.scales), up(v.quants), up(v.scales), up(table)]
+    return q16, k, v, bufs, L
+
+
+@pytest.mark.parametrize("m,q0,page", [(64, 0, 64), (256, 512, 256), (100, 333, 64)])
+def test_paged_q8_prefill_small(ctx, m, q0, page):
+    q16, k, v, bufs, L = _paged_prefill(ctx, 0x5602 + m, m, q0, page=page)
+    want = O.attention_f64(q16.astype(np.float32), k.deq16, v.deq16, m, q0, H, KV, D, SCALE)
+    rows = -(-L // 64) * 64
+    k_lin, v_lin = ctx.new_buffer(rows * KV * D, np.uint16), ctx.new_buffer(rows * KV * D, np.uint16)
+    out = ctx.new_buffer(m * H * D, np.float32)
+    step = _step(ctx, q0=q0, kv_len_global=L, pos=q0)
+    ctx.dispatch_blocking(ctx.load_kernel("attn_prefill_paged_q8kv_flash_d128"), bind(*bufs, k_lin, v_lin, out, step), (SCALE, page),
+                          [KV, m, 1])
+    assert_close(out.read().reshape(m, H, D), want, what=f"paged flash m={m} q0={q0}")
+    # bit-exact Q8_0 dequantisation and page-table indexing: the linear scratch holds f16(scale*q)
+    got_k = O.f16_bits_to_f32(k_lin.read()).reshape(rows, KV, D)[:L]
+    assert np.array_equal(got_k, k.deq16)
+    out_s = ctx.new_buffer(m * H * D, np.float32)
+    ctx.dispatch_blocking(ctx.load_kernel("attn_prefill_paged_q8kv_scalar_d128"), bind(*bufs, out_s, step), (SCALE, page), [KV, m, 1])
+    assert_close(out_s.read().reshape(m, H, D), want, what=f"paged scalar m={m} q0={q0}")
+
+
+def test_paged_q8_prefill_8k_identity_table_sampled(ctx):
+    """BASELINE config 2: 8192 x 8192 causal, Q8_0 K/V in 256-token pages, identity table.  The
+    f64 oracle is evaluated on a seeded sample of query rows (all heads)."""
+    m, q0 = 8192, 0
+    q16, k, v, bufs, L = _paged_prefill(ctx, 0x5602, m, q0, identity=True)
+    k_lin, v_lin = ctx.new_buffer(L * KV * D, np.uint16), ctx.new_buffer(L * KV * D, np.uint16)
+    out = ctx.new_buffer(m * H * D, np.float32)
+    step = _step(ctx, q0=q0, kv_len_global=L)
+    ctx.dispatch_blocking(ctx.load_kernel("attn_prefill_paged_q8kv_flash_d128"), bind(*bufs, k_lin, v_lin, out, step), (SCALE, PAGE),
+                          [KV, m, 1])
+    got = out.read().reshape(m, H, D)
+    tokens = np.unique(np.concatenate([[0, 1, 63, 64, 65, 127, 128, 4095, 4096, 8191],
+                                       np.random.default_rng(2).integers(0, m, 40)])).astype(np.uint32)
+    want = O.attention_f64(q16.astype(np.float32), k.deq16, v.deq16, m, q0, H, KV, D, SCALE, tokens=tokens)
+    assert_close(got[tokens], want, what="cfg2 sampled rows")
+    assert np.all(np.isfinite(got))
