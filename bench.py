@@ -1,0 +1,501 @@
+#!/usr/bin/env python
+"""Benchmark of the attention hot path on B200.
+
+    python bench.py --gpus N --steps K --warmup W            # this library (CUDA, through the C ABI)
+    python bench.py --impl reference --gpus N --steps K ...  # the reference's math on the host cores
+
+Headline workload (BASELINE config 5a, the 128K-context case of the metric): a 4096-token query
+chunk at q0 = 126976 attends causally to 131072 cached tokens held as Q8_0 in 256-token pages
+behind a seeded random page table; 32 query / 16 kv heads, head_dim 128.  A step is one pass:
+dequantise-and-gather K and V, then the tcgen05 flash kernel.  With N GPUs the kv heads are split
+into N groups (strong scaling, no data-path collective).  The JSON line also carries the other
+BASELINE configs under "extra": config 2 (8192 x 8192 prefill), config 3 (32K decode), config 4
+(4-token verify at 64K) and config 5b (128K decode, sequence-split over the ranks with an NCCL
+all-gather of the (acc, m, l) partials and a rank-ordered combine).
+
+All inputs are synthetic: seeded N(0,1) rounded to f16, quantised on the device by this library's
+own kv_append_paged_q8_d128 (bit-exact with the oracle's quantiser, see tests/test_gpu_kv.py).
+"""
+from __future__ import annotations
+
+import argparse
+import json
+import math
+import os
+import subprocess
+import sys
+import tempfile
+import threading
+import time
+
+import numpy as np
+
+ROOT = os.path.dirname(os.path.abspath(__file__))
+sys.path.insert(0, ROOT)
+
+H, KV, D, G, PAGE = 32, 16, 128, 2, 256
+SCALE = 1.0 / math.sqrt(D)
+SEED = 0x5605
+
+
+def peaks():
+    """Measured denominators (driver-written MEASURED_PEAKS.json), else the pool's earlier measurement."""
+    p = os.path.join(ROOT, "MEASURED_PEAKS.json")
+    if os.path.exists(p):
+        d = json.load(open(p))
+        return {"hbm_gbs": d["hbm_gbs"], "tf_burst": d["bf16_tflops"], "tf_sustained": d["bf16_tflops_sustained"], "kind": "measured"}
+    return {"hbm_gbs": 6650.0, "tf_burst": 1590.0, "tf_sustained": 1400.0, "kind": "fallback"}
+
+
+def causal_pairs(m, q0):
+    return m * q0 + m * (m + 1) // 2
+
+
+# --------------------------------------------------------------------------------------------------
+# clocks during the timed region
+# --------------------------------------------------------------------------------------------------
+class ClockSampler:
+    Q = ("index,clocks.sm,clocks.max.sm,power.draw,clocks_event_reasons.active,clocks_event_reasons.hw_slowdown,"
+         "clocks_event_reasons.hw_thermal_slowdown,clocks_event_reasons.sw_thermal_slowdown,clocks_event_reasons.sw_power_cap")
+
+    def __init__(self, device):
+        self.device, self.proc, self.path = device, None, None
+
+    def __enter__(self):
+        try:
+            f = tempfile.NamedTemporaryFile("w", suffix=".csv", delete=False)
+            self.path = f.name
+            self.proc = subprocess.Popen(["nvidia-smi", f"--query-gpu={self.Q}", "--format=csv,noheader,nounits", "-lms", "100",
+                                          "-i", str(self.device)], stdout=f, stderr=subprocess.DEVNULL)
+        except Exception:
+            self.proc = None
+        return self
+
+    def __exit__(self, *a):
+        if self.proc:
+            time.sleep(0.15)
+            self.proc.terminate()
+            try:
+                self.proc.wait(timeout=5)
+            except Exception:
+                self.proc.kill()
+
+    def summary(self):
+        out = {"sm_mhz": None, "sm_max_mhz": None, "reasons": []}
+        try:
+            rows = [r.split(",") for r in open(self.path).read().strip().splitlines() if r.strip()]
+            sm = [float(r[1]) for r in rows]
+            out["sm_mhz"] = float(np.median(sm))
+            out["sm_max_mhz"] = float(rows[0][2])
+            out["power_w_max"] = max(float(r[3]) for r in rows)
+            names = ["hw_slowdown", "hw_thermal_slowdown", "sw_thermal_slowdown", "sw_power_cap"]
+            out["reasons"] = [n for i, n in enumerate(names) if any("Active" in r[5 + i] and "Not" not in r[5 + i] for r in rows)]
+            out["samples"] = len(rows)
+            os.unlink(self.path)
+        except Exception:
+            pass
+        return out
+
+
+# --------------------------------------------------------------------------------------------------
+# device-side workload construction
+# --------------------------------------------------------------------------------------------------
+class Dev:
+    """One rank's device state: a context on a torch stream, and helpers to wrap torch tensors."""
+
+    def __init__(self, local_rank):
+        import torch
+
+        import super_gemma_b200 as sg
+
+        self.torch, self.sg = torch, sg
+        torch.cuda.set_device(local_rank)
+        self.device = torch.device("cuda", local_rank)
+        self.stream = torch.cuda.Stream(self.device)
+        self.ctx = sg.GpuContext(local_rank, stream=self.stream.cuda_stream)
+        self.k = {}
+
+    def kernel(self, name):
+        if name not in self.k:
+            self.k[name] = self.ctx.load_kernel(name)
+        return self.k[name]
+
+    def wrap(self, t):
+        return self.ctx.adopt(t.data_ptr(), t.numel() * t.element_size(), np.uint8, keep=t)
+
+    def randn_f16(self, seed, *shape):
+        g = self.torch.Generator(device=self.device)
+        g.manual_seed(seed)
+        return self.torch.randn(*shape, generator=g, device=self.device, dtype=self.torch.float32).half()
+
+    def bind(self, *bufs):
+        return [self.sg.BufferBinding.buffer(i, b) for i, b in enumerate(bufs)]
+
+
+def build_q(dev, seed, m, heads):
+    """Q [m, len(heads), D]: each query head is seeded by its global index, so a rank that owns a
+    slice of the heads holds exactly the rows the 1-GPU run holds."""
+    t = dev.torch.empty(m, len(heads), D, dtype=dev.torch.float16, device=dev.device)
+    for j, h in enumerate(heads):
+        t[:, j] = dev.randn_f16(seed * 1000 + h, m, D)
+    return t
+
+
+def build_paged_kv(dev, seed, tokens, kv_heads, table, pool_pages):
+    """K and V of `tokens` logical tokens for the given global kv heads, quantised to Q8_0 and
+    scattered into paged pools through `table` by kv_append_paged_q8_d128."""
+    torch = dev.torch
+    n_kv = len(kv_heads)
+    row = n_kv * D
+    rows = pool_pages * PAGE
+    table_t = torch.from_numpy(table.astype(np.int32)).to(dev.device)
+    step = torch.zeros(4, dtype=torch.int32, device=dev.device)
+    pools = []
+    for which in range(2):
+        quants = torch.zeros(rows * row, dtype=torch.int8, device=dev.device)
+        scales = torch.zeros(rows * row // 32, dtype=torch.float16, device=dev.device)
+        src = torch.empty(tokens, n_kv, D, dtype=torch.float16, device=dev.device)
+        for j, h in enumerate(kv_heads):
+            src[:, j] = dev.randn_f16(seed * 1000 + 100 * (which + 1) + h, tokens, D)
+        torch.cuda.synchronize()
+        k = dev.kernel("kv_append_paged_q8_d128")
+        dev.ctx.dispatch_blocking(k, dev.bind(dev.wrap(src), dev.wrap(scales), dev.wrap(quants), dev.wrap(table_t), dev.wrap(step)),
+                                  (row, PAGE), k.groups_for(tokens * row // 32))
+        pools += [quants, scales]
+        del src
+    return pools[0], pools[1], pools[2], pools[3], table_t
+
+
+def fisher_yates(seed, n):
+    return np.random.default_rng(seed).permutation(n).astype(np.uint32)
+
+
+def timed(dev, fn, steps, warmup, dist=None, stamps_per_step=1):
+    """W untimed steps, then K steps bracketed by barrier + synchronize; returns (max-over-ranks
+    seconds for the K steps, per-step stamp deltas in ns as array [K, stamps_per_step])."""
+    torch = dev.torch
+    for _ in range(warmup):
+        fn(None, 0)
+    dev.ctx.sync()
+    timer = dev.ctx.new_timer(steps * stamps_per_step + 1)
+    if dist is not None:
+        dist.barrier()
+    torch.cuda.synchronize()
+    before = dev.ctx.launch_count
+    for i in range(steps):
+        fn(timer, i * stamps_per_step)
+    timer.stamp(steps * stamps_per_step)
+    dev.ctx.sync()
+    torch.cuda.synchronize()
+    launches = dev.ctx.launch_count - before
+    ns = np.array(timer.read_ns(), dtype=np.float64)
+    total_s = (ns[-1] - ns[0]) * 1e-9
+    if dist is not None:
+        t = torch.tensor([total_s], dtype=torch.float64, device=dev.device)
+        dist.all_reduce(t, op=dist.ReduceOp.MAX)
+        total_s = float(t.item())
+    return total_s, np.diff(ns).reshape(steps, stamps_per_step), launches
+
+
+# --------------------------------------------------------------------------------------------------
+# workloads
+# --------------------------------------------------------------------------------------------------
+def run_prefill(dev, rank, world, steps, warmup, dist, m, ctx_len, identity, seed, e2e=False, stamps=True):
+    """Chunked prefill of m tokens at q0 = ctx_len - m over a ctx_len-token paged Q8_0 cache;
+    kv heads split over the ranks.  Returns a dict of measurements."""
+    torch = dev.torch
+    q0 = ctx_len - m
+    kvh = list(range(rank * KV // world, (rank + 1) * KV // world))
+    qh = [h * G + g for h in kvh for g in range(G)]
+    n_kv = len(kvh)
+    n_pages = ctx_len // PAGE
+    table = np.arange(n_pages, dtype=np.uint32) if identity else fisher_yates(seed + 0x100, n_pages)
+    kq, ks, vq, vs, table_t = build_paged_kv(dev, seed, ctx_len, kvh, table, n_pages)
+    q = build_q(dev, seed, m, qh)
+    k_lin = torch.zeros(ctx_len * n_kv * D, dtype=torch.float16, device=dev.device)
+    v_lin = torch.zeros_like(k_lin)
+    out = torch.zeros(m, len(qh), D, dtype=torch.float32, device=dev.device)
+    step_t = torch.tensor([q0, 0, ctx_len, q0], dtype=torch.int32, device=dev.device)
+    torch.cuda.synchronize()
+    W = dev.wrap
+    b_q, b_kq, b_ks, b_vq, b_vs, b_tab, b_kl, b_vl, b_out, b_step = map(W, (q, kq, ks, vq, vs, table_t, k_lin, v_lin, out, step_t))
+    deq, flash = dev.kernel("kv_dequant_paged_q8_d128"), dev.kernel("attn_prefill_flash_f16_d128")
+    row = n_kv * D
+
+    def step(timer, base):
+        if timer is not None:
+            timer.stamp(base)
+        dev.ctx.dispatch(deq, dev.bind(b_ks, b_kq, b_tab, b_kl, b_step), (row, PAGE), [1, 1, 1])
+        dev.ctx.dispatch(deq, dev.bind(b_vs, b_vq, b_tab, b_vl, b_step), (row, PAGE), [1, 1, 1])
+        if timer is not None:
+            timer.stamp(base + 1)
+        dev.ctx.dispatch(flash, dev.bind(b_q, b_kl, b_vl, b_out, b_step), (SCALE, 0), [n_kv, m, 1])
+
+    total_s, deltas, launches = timed(dev, step, steps, warmup, dist, stamps_per_step=2)
+    flop_total = 4.0 * D * causal_pairs(m, q0) * H
+    res = {"ms_per_step": total_s / steps * 1e3, "tflops": flop_total * steps / total_s / 1e12, "launches": launches,
+           "flash_ms": float(np.mean(deltas[:, 1])) * 1e-6, "dequant_ms": float(np.mean(deltas[:, 0])) * 1e-6,
+           "flop_per_rank": flop_total / world, "flop_total": flop_total}
+    res["sample"] = out[:: max(1, m // 7), 0, :4].float().cpu().numpy().tolist() if rank == 0 else None
+
+    if e2e:
+        # The same pass through the C ABI with HOST buffers: pinned Q, K/V pools, page table and step
+        # words go up every step, the f32 output comes back every step.
+        host = {n: torch.empty(t.shape, dtype=t.dtype).pin_memory() for n, t in
+                (("q", q), ("kq", kq), ("ks", ks), ("vq", vq), ("vs", vs), ("tab", table_t))}
+        for n, t in (("q", q), ("kq", kq), ("ks", ks), ("vq", vq), ("vs", vs), ("tab", table_t)):
+            host[n].copy_(t)
+        out_h = torch.empty(out.shape, dtype=out.dtype).pin_memory()
+        ups = [(b_q, host["q"]), (b_kq, host["kq"]), (b_ks, host["ks"]), (b_vq, host["vq"]), (b_vs, host["vs"]), (b_tab, host["tab"])]
+        L = dev.sg.lib()
+        h2d = sum(t.numel() * t.element_size() for _, t in ups) + 16
+        d2h = out_h.numel() * 4
+
+        def step_e2e(timer, base):
+            if timer is not None:
+                timer.stamp(base)
+            for buf, t in ups:
+                dev.sg.gpu._check(L.sgb_buffer_upload_async(buf._h, 0, t.data_ptr(), t.numel() * t.element_size()))
+            dev.sg.StepState(pos=q0, kv_len_global=ctx_len, q0=q0).write_to(b_step)
+            dev.ctx.dispatch(deq, dev.bind(b_ks, b_kq, b_tab, b_kl, b_step), (row, PAGE), [1, 1, 1])
+            dev.ctx.dispatch(deq, dev.bind(b_vs, b_vq, b_tab, b_vl, b_step), (row, PAGE), [1, 1, 1])
+            dev.ctx.dispatch(flash, dev.bind(b_q, b_kl, b_vl, b_out, b_step), (SCALE, 0), [n_kv, m, 1])
+            dev.sg.gpu._check(L.sgb_buffer_download_async(b_out._h, 0, out_h.data_ptr(), d2h))
+            dev.ctx.sync()
+
+        e_steps = max(2, min(steps, 5))
+        total_e, _, _ = timed(dev, step_e2e, e_steps, 1, dist)
+        res["e2e"] = {"value": flop_total * e_steps / total_e / 1e12, "unit": "TFLOP/s", "h2d_bytes_per_step": int(h2d * world),
+                      "d2h_bytes_per_step": int(d2h * world), "ms_per_step": total_e / e_steps * 1e3}
+    return res
+
+
+def run_decode(dev, rank, world, steps, warmup, dist, ctx_len, m_q, n_splits, seed, copies=4):
+    """Decode (m_q = 1) or verify (m_q = 4) over a ctx_len-token paged Q8_0 cache.  With world > 1
+    the sequence is split into contiguous page ranges; each rank merges its own splits to
+    (acc, m, l), the partials are all-gathered over NCCL and merged in rank order."""
+    torch = dev.torch
+    local_len = ctx_len // world
+    n_pages = local_len // PAGE
+    kvh = list(range(KV))
+    # distinct pools per launch rotate through HBM so that a 143 MB stream is not served from L2
+    pools = []
+    for c in range(copies if local_len * KV * (D + 8) * 2 < 512e6 else 2):
+        table = fisher_yates(seed + 0x100 + c, n_pages)
+        pools.append(build_paged_kv(dev, seed + 17 * c + 31 * rank, local_len, kvh, table, n_pages))
+    q = build_q(dev, seed, m_q, list(range(H)))
+    rows = m_q * H
+    part = torch.zeros(rows * n_splits * (D + 2), dtype=torch.float32, device=dev.device)
+    out = torch.zeros(rows * D, dtype=torch.float32, device=dev.device)
+    mine = torch.zeros(rows * (D + 2), dtype=torch.float32, device=dev.device)
+    gathered = torch.zeros(world * rows * (D + 2), dtype=torch.float32, device=dev.device)
+    step_t = torch.tensor([0, 0, local_len, 0], dtype=torch.int32, device=dev.device)
+    torch.cuda.synchronize()
+    W = dev.wrap
+    b_q, b_part, b_out, b_mine, b_gath, b_step = map(W, (q, part, out, mine, gathered, step_t))
+    b_pools = [tuple(W(t) for t in p) for p in pools]
+    dec = dev.kernel("attn_decode_paged_q8kv_d128" if m_q == 1 else "attn_verify_paged_q8kv_d128")
+    red, redp, comb = dev.kernel("attn_reduce_f32_d128"), dev.kernel("attn_reduce_partial_d128"), dev.kernel("attn_combine_ranks_d128")
+
+    def step(timer, base):
+        kq, ks, vq, vs, tab = b_pools[base % len(b_pools)]
+        if timer is not None:
+            timer.stamp(base)
+        dev.ctx.dispatch(dec, dev.bind(b_q, kq, ks, vq, vs, tab, b_part, b_step), (n_splits, SCALE, PAGE), [KV, n_splits, m_q])
+        if timer is not None:
+            timer.stamp(base + 1)
+        if world == 1:
+            dev.ctx.dispatch(red, dev.bind(b_part, b_out), n_splits, [rows, 1, 1])
+        else:
+            dev.ctx.dispatch(redp, dev.bind(b_part, b_mine), n_splits, [rows, 1, 1])
+            with torch.cuda.stream(dev.stream):
+                dist.all_gather_into_tensor(gathered, mine)
+            dev.ctx.dispatch(comb, dev.bind(b_gath, b_out), world, [rows, 1, 1])
+
+    total_s, deltas, launches = timed(dev, step, steps, warmup, dist, stamps_per_step=2)
+    kv_bytes = ctx_len * KV * (D + 8) * 2  # quants + scales, K and V
+    algo = kv_bytes + m_q * H * D * 2 + m_q * H * D * 4 + (ctx_len // PAGE) * 4
+    kern_us = float(np.median(deltas[:, 0])) * 1e-3
+    return {"us_per_step": total_s / steps * 1e6, "gbs": algo * steps / total_s / 1e9, "kernel_us": kern_us,
+            "kernel_gbs": (algo / world) / kern_us / 1e3, "algorithmic_bytes": algo, "n_splits": n_splits, "launches": launches}
+
+
+# --------------------------------------------------------------------------------------------------
+# CPU arm: the oracle's f32 shader-order flash prefill on a bounded sample of the headline workload
+# --------------------------------------------------------------------------------------------------
+def cpu_prefill_sample(m, ctx_len, target_s, seed=SEED):
+    """Times oracle/sg_oracle.c:sgo_prefill_flash_f32 (OpenMP over (token, head)) on sampled query
+    rows of the headline workload and returns TFLOP/s over the sampled rows."""
+    from oracle import sg_oracle as O
+
+    q0 = ctx_len - m
+    rng = np.random.default_rng(seed)
+    n_kv = KV
+    # The CPU sample uses its own seeded N(0,1) data of the same shape and layout (quantised by the
+    # oracle); throughput does not depend on the values.
+    keys = ctx_len
+    x = rng.standard_normal((2, keys, n_kv * D), dtype=np.float32).astype(np.float16).astype(np.float32)
+    ks_, kq_ = O.quant_q8_0(x[0])
+    vs_, vq_ = O.quant_q8_0(x[1])
+    del x
+    table = fisher_yates(seed + 0x100, keys // PAGE)
+    # scatter rows through the table so the oracle walks the same indirection
+    t = np.arange(keys)
+    phys = table[t // PAGE].astype(np.int64) * PAGE + t % PAGE
+    inv = np.empty(keys, np.int64)
+    inv[phys] = t
+    kq_p = np.ascontiguousarray(kq_.reshape(keys, -1)[inv])
+    ks_p = np.ascontiguousarray(ks_.reshape(keys, -1)[inv])
+    vq_p = np.ascontiguousarray(vq_.reshape(keys, -1)[inv])
+    vs_p = np.ascontiguousarray(vs_.reshape(keys, -1)[inv])
+    ksrc = O.KvSrc(quants=kq_p, scales=ks_p, page_table=table, page=PAGE, round_f16=True)
+    vsrc = O.KvSrc(quants=vq_p, scales=vs_p, page_table=table, page=PAGE, round_f16=True)
+    q16 = rng.standard_normal((m, H, D), dtype=np.float32).astype(np.float16)
+    cores = O.num_threads()
+
+    def run(tokens):
+        t0 = time.perf_counter()
+        O.prefill_flash_f32(q16.view(np.uint16), ksrc, vsrc, m, q0, H, n_kv, D, 0, SCALE, 64, tokens=tokens)
+        dt = time.perf_counter() - t0
+        pairs = sum(q0 + int(i) + 1 for i in tokens)
+        return dt, 4.0 * D * pairs * H
+
+    n0 = max(1, cores // H)
+    dt, _ = run(np.arange(n0, dtype=np.uint32) * (m // max(n0, 1)))
+    n = int(max(n0, min(m, n0 * target_s / max(dt, 1e-3))))
+    tokens = np.linspace(0, m - 1, n).astype(np.uint32)
+    dt, flop = run(tokens)
+    return {"value": flop / dt / 1e12, "unit": "TFLOP/s", "cores": cores, "kind": "port",
+            "sample": f"{n} of {m} query tokens x {H} heads of the headline workload ({dt:.1f} s of oracle/sg_oracle.c "
+                      f"sgo_prefill_flash_f32, OpenMP)", "seconds": dt}, (lambda: run(tokens))
+
+
+def reference_arm(args):
+    rank = int(os.environ.get("RANK", "0"))
+    if rank != 0:
+        return
+    m, ctx_len = args.m, args.ctx
+    base, rerun = cpu_prefill_sample(m, ctx_len, target_s=max(2.0, 60.0 / max(1, args.steps + args.warmup)))
+    for _ in range(max(0, args.warmup - 1)):
+        rerun()
+    t0 = time.perf_counter()
+    flop = 0.0
+    for _ in range(args.steps):
+        _, f = rerun()
+        flop += f
+    dt = time.perf_counter() - t0
+    v = flop / dt / 1e12
+    base["value"] = v
+    line = {"impl": "reference", "metric": "prefill_attn_tflops", "value": v, "unit": "TFLOP/s", "n_gpus": args.gpus,
+            "steps": args.steps, "warmup": args.warmup, "ms_per_step": dt / args.steps * 1e3, "higher_is_better": True,
+            "scaling": "strong", "vs_baseline": None, "dtype": "f32", "data": "synthetic",
+            "config": workload_config(args, 1), "cpu_baseline": base,
+            "e2e": {"value": v, "unit": "TFLOP/s", "h2d_bytes_per_step": 0, "d2h_bytes_per_step": 0}}
+    print(json.dumps(line), flush=True)
+
+
+def workload_config(args, world):
+    return {"workload": f"BASELINE config 5a: chunked prefill, {args.m} queries at q0={args.ctx - args.m} over {args.ctx} cached "
+                        f"Q8_0 tokens (256-token pages, seeded random page table), 32 q / 16 kv heads, head_dim 128, causal",
+            "m": args.m, "ctx": args.ctx, "kv_heads_per_gpu": KV // world, "parallelism": f"kv-head groups x{world}",
+            "l2": "K/V pools plus the f16 scratch written and re-read each step exceed the 126 MB L2; no flush"}
+
+
+def main():
+    ap = argparse.ArgumentParser()
+    ap.add_argument("--gpus", type=int, default=1)
+    ap.add_argument("--steps", type=int, default=10)
+    ap.add_argument("--warmup", type=int, default=3)
+    ap.add_argument("--impl", default="b200", choices=["b200", "reference"])
+    ap.add_argument("--m", type=int, default=4096)
+    ap.add_argument("--ctx", type=int, default=131072)
+    ap.add_argument("--no-extra", action="store_true", help="headline workload only")
+    ap.add_argument("--no-cpu", action="store_true", help="skip the CPU baseline leg")
+    args = ap.parse_args()
+    args.warmup = max(args.warmup, 3) if args.impl == "b200" else args.warmup
+
+    if args.impl == "reference":
+        reference_arm(args)
+        return
+
+    import torch
+
+    rank = int(os.environ.get("RANK", "0"))
+    world = int(os.environ.get("WORLD_SIZE", "1"))
+    local_rank = int(os.environ.get("LOCAL_RANK", "0"))
+    dist = None
+    if world > 1:
+        import torch.distributed as dist_mod
+
+        os.environ.setdefault("MASTER_ADDR", "127.0.0.1")
+        torch.cuda.set_device(local_rank)
+        dist_mod.init_process_group("nccl", device_id=torch.device("cuda", local_rank))
+        dist = dist_mod
+    if world != args.gpus and rank == 0:
+        print(f"note: --gpus {args.gpus} but WORLD_SIZE={world}; launch N > 1 with torch.distributed.run", file=sys.stderr)
+    if KV % world:
+        raise SystemExit("the kv heads (16) must divide over the ranks")
+
+    dev = Dev(local_rank)  # raises without the CUDA library or a B200: there is no fallback
+    pk = peaks()
+    with ClockSampler(local_rank) as clocks:
+        head = run_prefill(dev, rank, world, args.steps, args.warmup, dist, args.m, args.ctx, False, SEED, e2e=True)
+    clk = clocks.summary()
+    torch.cuda.empty_cache()
+
+    extra = {}
+    if not args.no_extra:
+        try:
+            if world == 1:
+                c2 = run_prefill(dev, rank, world, max(3, args.steps), 3, dist, 8192, 8192, True, 0x5602)
+                extra["config2_prefill_8192"] = {"tflops": c2["tflops"], "ms_per_step": c2["ms_per_step"], "flash_ms": c2["flash_ms"],
+                                                 "frac_of_burst_peak": c2["flop_total"] / (c2["flash_ms"] * 1e-3) / 1e12 / pk["tf_burst"]}
+                torch.cuda.empty_cache()
+                best = None
+                for ns in (32, 64):
+                    d3 = run_decode(dev, rank, world, 40, 5, dist, 32768, 1, ns, 0x5603)
+                    if best is None or d3["kernel_us"] < best["kernel_us"]:
+                        best = d3
+                best["hbm_frac_kernel"] = best["kernel_gbs"] / pk["hbm_gbs"]
+                extra["config3_decode_32k"] = best
+                torch.cuda.empty_cache()
+                d4 = run_decode(dev, rank, world, 40, 5, dist, 65536, 4, 64, 0x5604, copies=2)
+                d4["hbm_frac_kernel"] = d4["kernel_gbs"] / pk["hbm_gbs"]
+                extra["config4_verify_64k"] = d4
+                torch.cuda.empty_cache()
+            d5 = run_decode(dev, rank, world, 40, 5, dist, 131072, 1, 64 if world < 4 else 32, 0x5605, copies=2)
+            d5["hbm_frac_kernel"] = d5["kernel_gbs"] / pk["hbm_gbs"]
+            extra["config5b_decode_128k"] = d5
+        except Exception as e:  # the headline line must still be printed
+            extra["error"] = repr(e)
+
+    if rank == 0:
+        cpu = None
+        if not args.no_cpu and world == 1:
+            try:
+                cpu, _ = cpu_prefill_sample(args.m, args.ctx, target_s=15.0)
+            except Exception as e:
+                cpu = {"error": repr(e)}
+        flash_s = head["flash_ms"] * 1e-3
+        achieved = head["flop_per_rank"] / flash_s / 1e12
+        long_run = head["ms_per_step"] * args.steps > 1000.0
+        peak = pk["tf_sustained"] if long_run else pk["tf_burst"]
+        line = {
+            "metric": "prefill_attn_tflops", "value": head["tflops"], "unit": "TFLOP/s", "n_gpus": world, "steps": args.steps,
+            "warmup": args.warmup, "ms_per_step": head["ms_per_step"], "higher_is_better": True, "scaling": "strong",
+            "vs_baseline": None, "dtype": "f16 x f16 -> f32 (Q8_0 K/V dequantised to f16)", "data": "synthetic",
+            "config": workload_config(args, world),
+            "roofline": {"bound": "tensor", "kernel": "flash_prefill_kernel (attn_prefill_flash_f16_d128)", "achieved": achieved,
+                         "peak": peak, "unit": "TFLOP/s", "frac": achieved / peak,
+                         "peak_kind": f"{pk['kind']} bf16 {'sustained' if long_run else 'burst'}", "traffic": None,
+                         "ms_per_launch": head["flash_ms"], "dequant_ms_per_step": head["dequant_ms"]},
+            "cpu_baseline": cpu, "e2e": head.get("e2e"), "gpu_launches": int(head["launches"]), "clocks": clk, "extra": extra,
+        }
+        print(json.dumps(line), flush=True)
+    if dist is not None:
+        dist.barrier()
+        dist.destroy_process_group()
+
+
+if __name__ == "__main__":
+    main()
