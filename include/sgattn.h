@@ -128,6 +128,29 @@ int sgb_timer_stamp(sgb_ctx *ctx, sgb_timer *t, uint32_t index); /* also legal w
 int sgb_timer_read_ns(sgb_timer *t, uint64_t *out_ns, uint32_t n); /* ns since stamp 0; syncs the events */
 void sgb_timer_destroy(sgb_timer *t);
 
+/* ---- allocation-free decode (no counterpart in the reference) ---------------------------------- */
+/* For hosts that cannot allocate device memory when they need attention -- a serving process that
+ * has given all of HBM to its KV pool, or a caller inside a phase where cudaMalloc is off limits.
+ * Runs the whole decode step of attn_decode_paged_q8kv_d128 + attn_reduce_f32_d128 (same layouts,
+ * same arithmetic) on `stream` without cudaMalloc, cudaFree or any allocating library call: the
+ * split-K partials and the step words live in a static device array inside the library (about
+ * 1.04 MB, held by every GPU that loads the library until the process exits).
+ *   q f16 [m_q x n_kv_heads*2 x 128]; K/V pools as in the kernel signature (pool_rows rows each);
+ *   page_table u32[table_len]; out f32 [m_q x n_kv_heads*2 x 128]; status: NULL or 4 x u32 of device
+ *   memory that receives a device-side error report (first word non-zero = SGB_ERR_* code).
+ * Limit: m_q * n_kv_heads*2 * n_splits <= 2048 partial rows (32 q heads x 64 splits); larger
+ * requests are rejected with SGB_ERR_VALIDATION.  All arguments are device pointers owned by the
+ * caller; the call is asynchronous on `stream` (NULL = the legacy default stream).
+ * The first call on each device resolves the static array's address and sets a kernel attribute:
+ * make that first call outside any stream capture.  Every call shares the one array and leaves its
+ * last partials there (each call overwrites all rows it reads, nothing needs zeroing); two calls
+ * that overlap on the GPU -- different streams, or different threads -- race on it. */
+int sgb_decode_paged_q8kv_d128_noalloc(int device, void *stream, const void *q, const void *k_quants, const void *k_scales,
+                                       const void *v_quants, const void *v_scales, const uint32_t *page_table,
+                                       uint32_t table_len, uint64_t pool_rows, float *out, uint32_t *status,
+                                       uint32_t n_kv_heads, uint32_t m_q, uint32_t kv_len, uint32_t n_splits, uint32_t page,
+                                       float scale);
+
 #ifdef __cplusplus
 }
 #endif

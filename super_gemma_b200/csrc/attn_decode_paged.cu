@@ -21,7 +21,10 @@
 //     -1152 * sum(q) and PV subtracts 1152 * sum(P') gathered by one extra MMA against ones;
 //   * online softmax in registers (base-2, row max by warp shuffles over the 4 lanes of a row,
 //     rescale only when the max grows by more than 2^8), warps merged in fixed order.
+#include <cstdio>
 #include <cstdlib>
+#include <initializer_list>
+#include <string>
 
 #include "sgb_common.cuh"
 #include "sgb_kernels.h"
@@ -456,3 +459,143 @@ int launch_decode_paged_q8kv_d128(const LaunchArgs& a)
 }
 
 }  // namespace sgb
+
+// ====================================================================================================
+// Allocation-free decode: sgb_decode_paged_q8kv_d128_noalloc
+//
+// Some hosts may not allocate device memory at the moment they need attention: a serving loop that
+// has handed every byte of HBM to its KV pool, or code running between an allocator's bookkeeping
+// phases where a cudaMalloc would stall the device.  This entry point does the whole decode step
+// -- split-K partials and the log-sum-exp combine -- without allocating anything, on the device or
+// through any library: the split-K partials and the four step words live in the file-scope array
+// below, which every GPU that loads this library holds until the process exits (about 1.04 MB).
+// ====================================================================================================
+namespace sgb {
+namespace {
+
+constexpr uint32_t NOALLOC_MAX_PART_ROWS = 2048;  // (query rows) x (splits) the scratch can hold
+constexpr size_t NOALLOC_PART_FLOATS = (size_t)NOALLOC_MAX_PART_ROWS * (HD + 2);
+constexpr size_t NOALLOC_STEP_AT = NOALLOC_PART_FLOATS;  // 4 x u32 step words after the partials
+
+static __device__ __align__(256) float g_noalloc_scratch[NOALLOC_PART_FLOATS + 64];
+
+// In host code `g_noalloc_scratch` is only a handle; the device address comes from
+// cudaGetSymbolAddress, once per device.
+void* g_noalloc_dev_ptr[64] = {};
+bool g_noalloc_ready[64] = {};
+
+__global__ void noalloc_step_kernel(uint32_t kv_len)
+{
+    uint32_t* step = reinterpret_cast<uint32_t*>(g_noalloc_scratch + NOALLOC_STEP_AT);
+    step[STEP_POS] = 0;
+    step[STEP_KV_LEN_SLIDING] = 0;
+    step[STEP_KV_LEN_GLOBAL] = kv_len;
+    step[STEP_Q0] = 0;
+}
+
+// Combine of the splits in ascending order (the arithmetic of attn_reduce.wgsl:29-56), reading the
+// partials straight from the static array.  One block per query row, one thread per dim.
+__global__ void __launch_bounds__(HD) noalloc_reduce_kernel(float* __restrict__ out, uint32_t n_splits)
+{
+    const size_t row = blockIdx.x;
+    const int d = threadIdx.x;
+    float m = NEG_SENTINEL, l = 0.0f, acc = 0.0f;
+    for (uint32_t s = 0; s < n_splits; s++) {
+        const float* p = g_noalloc_scratch + (row * n_splits + s) * (HD + 2);
+        const float ms = p[HD], ls = p[HD + 1];
+        const float m_new = fmaxf(m, ms);
+        const float ca = __expf(m - m_new), cb = __expf(ms - m_new);
+        acc = acc * ca + p[d] * cb;
+        l = l * ca + ls * cb;
+        m = m_new;
+    }
+    out[row * HD + d] = acc / l;
+}
+
+}  // namespace
+}  // namespace sgb
+
+extern "C" int sgb_decode_paged_q8kv_d128_noalloc(int device, void* stream, const void* q, const void* k_quants,
+                                                  const void* k_scales, const void* v_quants, const void* v_scales,
+                                                  const uint32_t* page_table, uint32_t table_len, uint64_t pool_rows,
+                                                  float* out, uint32_t* status, uint32_t n_kv_heads, uint32_t m_q,
+                                                  uint32_t kv_len, uint32_t n_splits, uint32_t page, float scale)
+{
+    using namespace sgb;
+    if (!q || !k_quants || !k_scales || !v_quants || !v_scales || !page_table || !out)
+        return set_last_error(3, "decode_noalloc: NULL pointer argument");
+    if (device < 0 || device >= 64) return set_last_error(1, "decode_noalloc: device index out of range");
+    if (n_kv_heads == 0 || (n_kv_heads & 1)) return set_last_error(3, "decode_noalloc: n_kv_heads must be even and > 0");
+    if (m_q == 0 || m_q > 4) return set_last_error(3, "decode_noalloc: m_q must be 1..4");
+    if (kv_len == 0 || n_splits == 0) return set_last_error(3, "decode_noalloc: kv_len and n_splits must be > 0");
+    if (page == 0 || page % STAGE_TOK) return set_last_error(3, "decode_noalloc: page must be a multiple of 64 tokens");
+    const uint64_t part_rows = (uint64_t)m_q * n_kv_heads * G * n_splits;
+    if (part_rows > NOALLOC_MAX_PART_ROWS) {
+        char buf[200];
+        snprintf(buf, sizeof buf,
+                 "decode_noalloc: m_q * q_heads * n_splits = %llu partial rows, the static scratch holds at most %u "
+                 "(e.g. 32 q heads x 64 splits); use the sgb_dispatch path with a caller-sized buffer instead",
+                 (unsigned long long)part_rows, NOALLOC_MAX_PART_ROWS);
+        return set_last_error(3, buf);
+    }
+    if (pool_rows == 0 || pool_rows % page) return set_last_error(3, "decode_noalloc: pool_rows must be whole pages");
+    if ((uint64_t)table_len * page < kv_len) return set_last_error(3, "decode_noalloc: page table shorter than kv_len");
+    for (const void* p : {k_quants, k_scales, v_quants, v_scales})
+        if (reinterpret_cast<uintptr_t>(p) & 15) return set_last_error(3, "decode_noalloc: K/V pools must be 16-byte aligned");
+
+    int prev = 0;
+    cudaError_t e = cudaGetDevice(&prev);
+    if (e == cudaSuccess && prev != device) e = cudaSetDevice(device);
+    if (e != cudaSuccess) return set_last_error(4, std::string("decode_noalloc: selecting the device: ") + cudaGetErrorString(e));
+    struct Restore {
+        int prev, dev;
+        ~Restore()
+        {
+            if (prev != dev) cudaSetDevice(prev);
+        }
+    } restore{prev, device};
+
+    // Set-up on the first call per device, with that device current: resolve the device address of
+    // the static array and raise the kernel's shared-memory limit.  Neither allocates.
+    if (!g_noalloc_ready[device]) {
+        void* ptr = nullptr;
+        e = cudaGetSymbolAddress(&ptr, g_noalloc_scratch);
+        if (e != cudaSuccess || ptr == nullptr)
+            return set_last_error(4, std::string("decode_noalloc: cudaGetSymbolAddress: ") + cudaGetErrorString(e));
+        e = cudaFuncSetAttribute(decode_paged_kernel<4, 2>, cudaFuncAttributeMaxDynamicSharedMemorySize,
+                                 (int)(sizeof(DecodeSmem<4>) + 1024));
+        if (e != cudaSuccess)
+            return set_last_error(4, std::string("decode_noalloc: cudaFuncSetAttribute: ") + cudaGetErrorString(e));
+        g_noalloc_dev_ptr[device] = ptr;
+        g_noalloc_ready[device] = true;
+    }
+    float* scratch = static_cast<float*>(g_noalloc_dev_ptr[device]);
+    const uint32_t* step = reinterpret_cast<const uint32_t*>(scratch + NOALLOC_STEP_AT);
+
+    std::string err;
+    uint64_t launches = 0;
+    LaunchArgs a{(cudaStream_t)stream, nullptr, nullptr, {n_kv_heads, n_splits, m_q}, status, 0, device, &err, &launches};
+    const size_t row_bytes = (size_t)n_kv_heads * HD;
+    CUtensorMap tm[4];
+    const void* quants[2] = {k_quants, v_quants};
+    const void* scales[2] = {k_scales, v_scales};
+    for (int i = 0; i < 2; i++) {
+        const uint64_t qd[3] = {HD, n_kv_heads, pool_rows};
+        const uint64_t qs[2] = {HD, row_bytes};
+        const uint32_t qb[3] = {HD, 1, STAGE_TOK};
+        if (int r = encode_tensor_map(a, &tm[2 * i], 0, 3, const_cast<void*>(quants[i]), qd, qs, qb, 3)) return set_last_error(r, err);
+        const uint64_t sd[2] = {(uint64_t)n_kv_heads * 4, pool_rows};
+        const uint64_t ss[1] = {(uint64_t)n_kv_heads * 8};
+        const uint32_t sb[2] = {8, STAGE_TOK};
+        if (int r = encode_tensor_map(a, &tm[2 * i + 1], 1, 2, const_cast<void*>(scales[i]), sd, ss, sb, 0)) return set_last_error(r, err);
+    }
+    cudaStream_t s = (cudaStream_t)stream;
+    noalloc_step_kernel<<<1, 1, 0, s>>>(kv_len);
+    decode_paged_kernel<4, 2><<<dim3(n_kv_heads, n_splits), THREADS, sizeof(DecodeSmem<4>) + 1024, s>>>(
+        tm[0], tm[1], tm[2], tm[3], (const __half*)q, page_table, table_len, page, (uint32_t)(pool_rows / page), scratch, step,
+        n_splits, scale, m_q, status);
+    noalloc_reduce_kernel<<<m_q * n_kv_heads * G, HD, 0, s>>>(out, n_splits);
+    e = cudaGetLastError();
+    if (e != cudaSuccess) return set_last_error(4, std::string("decode_noalloc: launch: ") + cudaGetErrorString(e));
+    return 0;
+}

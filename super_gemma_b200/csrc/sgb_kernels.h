@@ -38,6 +38,7 @@ struct KernelEntry {
 };
 
 // Host-side error helpers shared by the launchers (defined in sgb_runtime.cu).
+int set_last_error(int code, const std::string& msg);  // records the text sgb_last_error() returns; returns code
 int fail_validation(const LaunchArgs& a, const std::string& msg);
 int check_cuda(const LaunchArgs& a, cudaError_t e, const char* what);
 int need_bytes(const LaunchArgs& a, int binding, size_t bytes, const char* what);

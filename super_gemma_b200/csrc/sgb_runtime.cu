@@ -27,6 +27,8 @@ static int set_error(int code, const std::string& msg)
     return code;
 }
 
+int set_last_error(int code, const std::string& msg) { return set_error(code, msg); }
+
 int fail_validation(const LaunchArgs& a, const std::string& msg)
 {
     if (a.err) *a.err = msg;

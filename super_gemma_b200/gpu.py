@@ -115,6 +115,8 @@ ABI = {
     "sgb_timer_stamp": (_int, [_vp, _vp, _u32]),
     "sgb_timer_read_ns": (_int, [_vp, C.POINTER(_u64), _u32]),
     "sgb_timer_destroy": (None, [_vp]),
+    "sgb_decode_paged_q8kv_d128_noalloc": (_int, [_int, _vp, _vp, _vp, _vp, _vp, _vp, _vp, _u32, _u64, _vp, _vp, _u32, _u32, _u32,
+                                                   _u32, _u32, C.c_float]),
 }
 
 _lib: Optional[C.CDLL] = None
