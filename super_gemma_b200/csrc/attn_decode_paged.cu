@@ -7,20 +7,25 @@
 // reference's; row = i * H + qh for query token i.
 //
 // Design (HBM-bound: 17/16 byte per K/V element is all that has to move):
-//   * one CTA per (kv head, split); a producer warp streams 64-token stages of K quants, K scales,
-//     V quants, V scales with TMA into a ring of shared-memory stages (mbarrier full/empty pairs),
-//     translating logical tokens through the page table once per stage;
-//   * four consumer warps each own 16 tokens of a stage.  int8 bytes are turned into exact f16
-//     integers straight out of shared memory with byte permutes (0x6400 | (q ^ 0x80) = q + 1152)
-//     and fed to mma.sync m16n8k16 -- the tile is (8 query rows) x (16 tokens), far below the
-//     64-row minimum of tcgen05, so the warp-level MMA is the right tool here;
+//   * one warp per (kv head, split), four warps (four adjacent kv heads) per CTA, so a token row is
+//     fetched as 4 x 128 adjacent bytes of quants at about the same time.  Every warp runs its own
+//     pipeline: lane 0 issues the TMA loads of its head's 16-token stages (K quants, V quants, and
+//     the 16-byte scale pairs of its head and its neighbour) NSTAGES ahead, through the page
+//     table, into the warp's private ring of shared-memory stages; the only synchronisation is the
+//     warp's own "full" mbarrier per stage -- no producer warp, no cross-warp barrier;
+//   * a warp turns the int8 bytes of its head into exact f16 integers straight out of
+//     shared memory (ldmatrix, plain for K and transposed for V, then one byte permute per pair:
+//     0x6400 | (q ^ 0x80) = q + 1152) and feeds mma.sync m16n8k16 with the 16 tokens (QK^T) or 16
+//     dims (PV) as the M side and the <= 8 query rows as N, so no accumulator row is dead; the
+//     tile is far below the 64-row minimum of tcgen05, so the warp-level MMA is the right tool;
 //   * the per-block scales never touch the int8 data: QK^T is accumulated per 32-wide block and
 //     multiplied by f32(scale) afterwards (sum_b s_b * sum_d q_d k_d == sum_d q_d (s_b k_d), i.e.
 //     the reference's exact product f32(scale)*f32(q), no f16 re-rounding); for PV the scale is
 //     folded into P.  The +1152 offsets are removed exactly: the QK accumulator starts at
 //     -1152 * sum(q) and PV subtracts 1152 * sum(P') gathered by one extra MMA against ones;
-//   * online softmax in registers (base-2, row max by warp shuffles over the 4 lanes of a row,
-//     rescale only when the max grows by more than 2^8), warps merged in fixed order.
+//   * online softmax in registers (base 2, row max by warp shuffles over the 4 lanes of a row,
+//     rescale only when the max grows by more than 2^8).  A head's tokens are walked by one warp
+//     in order, so the partials need no cross-warp merge and reruns are bit-identical.
 #include <cstdio>
 #include <cstdlib>
 #include <initializer_list>
@@ -35,44 +40,75 @@ namespace {
 
 constexpr int HD = 128;
 constexpr int G = 2;                     // query heads per kv head
-constexpr int STAGE_TOK = 64;            // tokens per pipeline stage
-constexpr int CONSUMER_WARPS = 4;        // 16 tokens each
-constexpr int THREADS = (CONSUMER_WARPS + 1) * 32;
-constexpr int MAX_ROWS = 8;              // query rows in the MMA tile = m_q * G, m_q <= 4
-constexpr uint32_t Q_TILE_BYTES = STAGE_TOK * 128;
-constexpr uint32_t S_TILE_BYTES = STAGE_TOK * 16;
-constexpr uint32_t STAGE_BYTES = 2 * Q_TILE_BYTES + 2 * S_TILE_BYTES;
+constexpr int STAGE_TOK = 16;            // tokens per pipeline stage = one MMA tile per warp
+constexpr uint32_t HEAD_TILE = STAGE_TOK * 128;  // one head's quants of a stage: [16 tokens][128 B]
 constexpr uint32_t MAGIC = 0x64646464u;  // high byte of f16 1024.0
 constexpr float OFFSET = 1152.0f;        // 1024 + 128
 constexpr float RESCALE_T = 8.0f;        // lazy-rescale threshold, log2 units
 
+constexpr int WPC = 4;                   // warps (kv heads) per CTA
+constexpr uint32_t SCALE_TILE = STAGE_TOK * 16;  // [16 tokens][2 heads][4 f16]
+constexpr uint32_t STAGE_BYTES = 2 * HEAD_TILE + 2 * SCALE_TILE;
+
 template <int NSTAGES>
 struct __align__(1024) DecodeSmem {
-    uint8_t kq[NSTAGES][Q_TILE_BYTES];   // [64 tokens][128 B], 128-byte swizzled by TMA
-    uint8_t vq[NSTAGES][Q_TILE_BYTES];
-    uint8_t ks[NSTAGES][S_TILE_BYTES];   // [64 tokens][8 f16]: scales of a pair of kv heads
-    uint8_t vs[NSTAGES][S_TILE_BYTES];
-    float merge[CONSUMER_WARPS][MAX_ROWS][HD + 2];
-    uint64_t full[NSTAGES];
-    uint64_t empty[NSTAGES];
+    uint8_t kq[WPC][NSTAGES][HEAD_TILE];   // 128-byte swizzled by TMA
+    uint8_t vq[WPC][NSTAGES][HEAD_TILE];
+    uint8_t ks[WPC][NSTAGES][SCALE_TILE];
+    uint8_t vs[WPC][NSTAGES][SCALE_TILE];
+    uint64_t full[WPC][NSTAGES];
 };
 
-// mma.sync m16n8k16 with only the top 8 rows of A in use (rows 8..15 are zero).  The bottom half of
-// the accumulator is then c2 = c3 = 0 in and out, so it gets constants in and throw-away registers
-// out instead of live state: (c0, c1) is the accumulator of row g, columns 2*t4 and 2*t4 + 1.
-__device__ __forceinline__ void mma_top(float& c0, float& c1, uint32_t a0, uint32_t a2, uint32_t b0, uint32_t b1)
+__device__ __forceinline__ void mma16816(float (&c)[4], const uint32_t (&a)[4], uint32_t b0, uint32_t b1)
 {
-    float dead0, dead1;
-    asm volatile(
-        "mma.sync.aligned.m16n8k16.row.col.f32.f16.f16.f32 {%0,%1,%2,%3}, {%4,%5,%6,%5}, {%7,%8}, {%0,%1,%9,%9};"
-        : "+f"(c0), "+f"(c1), "=f"(dead0), "=f"(dead1)
-        : "r"(a0), "r"(0u), "r"(a2), "r"(b0), "r"(b1), "f"(0.0f));
+    asm("mma.sync.aligned.m16n8k16.row.col.f32.f16.f16.f32 {%0,%1,%2,%3}, {%4,%5,%6,%7}, {%8,%9}, {%0,%1,%2,%3};"
+        : "+f"(c[0]), "+f"(c[1]), "+f"(c[2]), "+f"(c[3])
+        : "r"(a[0]), "r"(a[1]), "r"(a[2]), "r"(a[3]), "r"(b0), "r"(b1));
+}
+// Transpose an 8x8 matrix of 16-bit elements held one row-pair per lane (the mma C/B layouts).
+__device__ __forceinline__ uint32_t movmatrix_trans(uint32_t a)
+{
+    uint32_t d;
+    asm("movmatrix.sync.aligned.m8n8.trans.b16 %0, %1;" : "=r"(d) : "r"(a));
+    return d;
 }
 
-__device__ __forceinline__ float quad_max(float v)
+__device__ __forceinline__ void ldsm_x4(uint32_t addr, uint32_t (&r)[4])
 {
-    v = fmaxf(v, __shfl_xor_sync(0xffffffffu, v, 1));
-    return fmaxf(v, __shfl_xor_sync(0xffffffffu, v, 2));
+    asm volatile("ldmatrix.sync.aligned.m8n8.x4.shared.b16 {%0,%1,%2,%3}, [%4];"
+                 : "=r"(r[0]), "=r"(r[1]), "=r"(r[2]), "=r"(r[3])
+                 : "r"(addr));
+}
+__device__ __forceinline__ void ldsm_x4_trans(uint32_t addr, uint32_t (&r)[4])
+{
+    asm volatile("ldmatrix.sync.aligned.m8n8.x4.trans.shared.b16 {%0,%1,%2,%3}, [%4];"
+                 : "=r"(r[0]), "=r"(r[1]), "=r"(r[2]), "=r"(r[3])
+                 : "r"(addr));
+}
+__device__ __forceinline__ uint2 lds_u2(uint32_t addr)
+{
+    uint2 v;
+    asm volatile("ld.shared.v2.u32 {%0,%1}, [%2];" : "=r"(v.x), "=r"(v.y) : "r"(addr));
+    return v;
+}
+__device__ __forceinline__ uint32_t hmul2_u32(uint32_t a, uint32_t b)
+{
+    __half2 r = __hmul2(*reinterpret_cast<__half2*>(&a), *reinterpret_cast<__half2*>(&b));
+    return *reinterpret_cast<uint32_t*>(&r);
+}
+
+// Reductions over the 8 lanes that share t4 (lane bits 2..4): the tokens of a tile.
+__device__ __forceinline__ float tok_max(float v)
+{
+    v = fmaxf(v, __shfl_xor_sync(0xffffffffu, v, 4));
+    v = fmaxf(v, __shfl_xor_sync(0xffffffffu, v, 8));
+    return fmaxf(v, __shfl_xor_sync(0xffffffffu, v, 16));
+}
+__device__ __forceinline__ float tok_sum(float v)
+{
+    v += __shfl_xor_sync(0xffffffffu, v, 4);
+    v += __shfl_xor_sync(0xffffffffu, v, 8);
+    return v + __shfl_xor_sync(0xffffffffu, v, 16);
 }
 __device__ __forceinline__ float quad_sum(float v)
 {
@@ -81,23 +117,20 @@ __device__ __forceinline__ float quad_sum(float v)
 }
 
 template <int NSTAGES, int MIN_CTAS>
-__global__ void __launch_bounds__(THREADS, MIN_CTAS) decode_paged_kernel(const __grid_constant__ CUtensorMap tm_kq,
-                                                               const __grid_constant__ CUtensorMap tm_ks,
-                                                               const __grid_constant__ CUtensorMap tm_vq,
-                                                               const __grid_constant__ CUtensorMap tm_vs,
-                                                               const __half* __restrict__ q,
-                                                               const uint32_t* __restrict__ page_table, uint32_t table_len,
-                                                               uint32_t page, uint32_t pool_pages, float* __restrict__ part,
-                                                               const uint32_t* __restrict__ step, uint32_t n_splits,
-                                                               float scale, uint32_t m_q, uint32_t* status)
+__global__ void __launch_bounds__(WPC * 32, MIN_CTAS)
+    decode_paged_kernel(const __grid_constant__ CUtensorMap tm_kq, const __grid_constant__ CUtensorMap tm_ks,
+                        const __grid_constant__ CUtensorMap tm_vq, const __grid_constant__ CUtensorMap tm_vs,
+                        const __half* __restrict__ q, const uint32_t* __restrict__ page_table, uint32_t table_len, uint32_t page,
+                        uint32_t pool_pages, float* __restrict__ part, const uint32_t* __restrict__ step, uint32_t n_kv,
+                        uint32_t n_splits, float scale, uint32_t m_q, uint32_t* status)
 {
     extern __shared__ uint8_t smem_raw[];
     using Smem = DecodeSmem<NSTAGES>;
     Smem& sm = *reinterpret_cast<Smem*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~uintptr_t(1023));
 
     const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
-    const int kvh = blockIdx.x, n_kv = gridDim.x, split = blockIdx.y;
-    const int n_q = n_kv * G;
+    const int kvh = blockIdx.x * WPC + warp, split = blockIdx.y;
+    const int n_q = (int)n_kv * G;
 
     const uint32_t kv_len = step[STEP_KV_LEN_GLOBAL];
     const uint32_t chunk = (kv_len + n_splits - 1) / n_splits;
@@ -106,268 +139,243 @@ __global__ void __launch_bounds__(THREADS, MIN_CTAS) decode_paged_kernel(const _
     const uint32_t s_begin = t_begin / STAGE_TOK;
     const uint32_t n_iter = t_begin < t_end ? (t_end + STAGE_TOK - 1) / STAGE_TOK - s_begin : 0;
 
-    if (threadIdx.x == 0) {
-        for (int i = 0; i < NSTAGES; i++) {
-            mbar_init(&sm.full[i], 1);
-            mbar_init(&sm.empty[i], CONSUMER_WARPS);
-        }
+    if (lane == 0) {
+        for (int i = 0; i < NSTAGES; i++) mbar_init(&sm.full[warp][i], 1);
         mbar_fence_init();
     }
-    __syncthreads();
+    __syncwarp();
+    if (kvh >= (int)n_kv) return;  // a CTA of the last group when n_kv is not a multiple of 4
 
-    if (warp == CONSUMER_WARPS) {
-        // ---------------- producer ----------------
-        if (lane == 0) {
-            tma_prefetch_desc(&tm_kq);
-            tma_prefetch_desc(&tm_ks);
-            tma_prefetch_desc(&tm_vq);
-            tma_prefetch_desc(&tm_vs);
-            bool failed = false;
-            for (uint32_t it = 0; it < n_iter; ++it) {
-                const int st = it % NSTAGES;
-                const uint32_t round = it / NSTAGES;
-                if (round > 0) mbar_wait(&sm.empty[st], (round - 1) & 1, status, 301, failed);
-                if (failed) break;
-                const uint32_t tok0 = (s_begin + it) * STAGE_TOK;
-                const uint32_t lp = tok0 / page;
-                uint32_t pp = 0;
-                if (lp < table_len) {
-                    pp = page_table[lp];
-                } else {
-                    report_error(status, DEV_ERR_BOUNDS, 302, lp, table_len);
-                }
-                if (pp >= pool_pages) {
-                    report_error(status, DEV_ERR_BOUNDS, 303, pp, pool_pages);
-                    pp = 0;
-                }
-                const int row = (int)(pp * page + tok0 % page);
-                mbar_arrive_expect_tx(&sm.full[st], STAGE_BYTES);
-                tma_load_3d(sm.kq[st], &tm_kq, &sm.full[st], 0, kvh, row);
-                tma_load_2d(sm.ks[st], &tm_ks, &sm.full[st], (kvh >> 1) * 8, row);
-                tma_load_3d(sm.vq[st], &tm_vq, &sm.full[st], 0, kvh, row);
-                tma_load_2d(sm.vs[st], &tm_vs, &sm.full[st], (kvh >> 1) * 8, row);
-            }
-            // Do not leave with copies in flight: wait (bounded) for the last use of every stage.
-            if (!failed) {
-                const uint32_t first = n_iter > (uint32_t)NSTAGES ? n_iter - NSTAGES : 0;
-                for (uint32_t it = first; it < n_iter; ++it)
-                    mbar_wait(&sm.full[it % NSTAGES], (it / NSTAGES) & 1, status, 304, failed);
-            }
+    // Physical page of the stage with index `stage` (tokens 16*stage ..), checked, never followed blindly.
+    auto lookup = [&](uint32_t stage) -> uint32_t {
+        const uint32_t lp = stage * STAGE_TOK / page;
+        uint32_t pp = 0;
+        if (lp < table_len) {
+            pp = __ldg(page_table + lp);
+        } else if (lane == 0) {
+            report_error(status, DEV_ERR_BOUNDS, 302, lp, table_len);
         }
-    } else {
-        // ---------------- consumers ----------------
-        const int g = lane >> 2, t4 = lane & 3;
-        const uint32_t rows = m_q * G;
-        const bool row_live = (uint32_t)g < rows;
-        const uint32_t qi = (uint32_t)g / G;
-        const int qh = kvh * G + g % G;
-        // Last key this row may see: kv_len - m_q + qi  (all of them when m_q == 1).
-        const int64_t vis_last = (int64_t)kv_len - (int64_t)m_q + (int64_t)qi;
-
-        // Q fragments of mma.m16n8k16 (A operand, rows = query rows; rows 8..15 are zero).  With the
-        // K bytes of a 32-wide block split 8 per lane (lane t4 holds bytes 8*t4 .. 8*t4+7), k-step s
-        // contracts dims 32b + 8*t4 + 4s + {0,1 | 2,3}.
-        uint32_t qa[4][2][2];
-        float cinit[4];
-        {
-            const __half* qrow = q + ((size_t)qi * n_q + qh) * HD;
-#pragma unroll
-            for (int b = 0; b < 4; b++) {
-                float sum = 0.0f;
-#pragma unroll
-                for (int s = 0; s < 2; s++) {
-                    uint2 w = make_uint2(0u, 0u);
-                    if (row_live) w = __ldg(reinterpret_cast<const uint2*>(qrow + 32 * b + 8 * t4 + 4 * s));
-                    qa[b][s][0] = w.x;
-                    qa[b][s][1] = w.y;
-                    const float2 f0 = __half22float2(*reinterpret_cast<const __half2*>(&w.x));
-                    const float2 f1 = __half22float2(*reinterpret_cast<const __half2*>(&w.y));
-                    sum += (f0.x + f0.y) + (f1.x + f1.y);
-                }
-                cinit[b] = -OFFSET * quad_sum(sum);
-            }
+        if (pp >= pool_pages) {
+            if (lane == 0) report_error(status, DEV_ERR_BOUNDS, 303, pp, pool_pages);
+            pp = 0;
         }
-
-        const float scale2 = scale * 1.4426950408889634f;
-        float m_run = NEG_SENTINEL, l_part = 0.0f;
-        float o[4][4][2];   // [block][i]: c0 -> dim 32b + 8*t4 + i, c1 -> dim 32b + 8*t4 + 4 + i
-        float osum[4];      // sum over tokens of P'_b for this row
-#pragma unroll
-        for (int b = 0; b < 4; b++) {
-            osum[b] = 0.0f;
-#pragma unroll
-            for (int i = 0; i < 4; i++) o[b][i][0] = o[b][i][1] = 0.0f;
-        }
-
-        bool failed = false;
-        for (uint32_t it = 0; it < n_iter; ++it) {
-            const int st = it % NSTAGES;
-            mbar_wait(&sm.full[st], (it / NSTAGES) & 1, status, 305, failed);
-            const uint32_t tile_tok0 = (s_begin + it) * STAGE_TOK + 16 * warp;
-            const int r0 = 16 * warp;  // first smem row of this warp's tile
-
-            // ---- S^T = Q K^T per block: rows = query rows, columns = tokens --------------------
-            float sacc[2][4][2];
-#pragma unroll
-            for (int j = 0; j < 2; j++) {
-                const int row = r0 + 8 * j + g;  // the token this lane supplies as B column n = g
-                const uint8_t* krow = sm.kq[st] + row * 128;
-                const int swz = row & 7;
-#pragma unroll
-                for (int b = 0; b < 4; b++) {
-                    const int c16 = (2 * b + (t4 >> 1)) ^ swz;
-                    uint2 w = *reinterpret_cast<const uint2*>(krow + c16 * 16 + (t4 & 1) * 8);
-                    w.x ^= 0x80808080u;
-                    w.y ^= 0x80808080u;
-                    sacc[j][b][0] = cinit[b];
-                    sacc[j][b][1] = cinit[b];
-                    mma_top(sacc[j][b][0], sacc[j][b][1], qa[b][0][0], qa[b][0][1], __byte_perm(w.x, MAGIC, 0x4140),
-                            __byte_perm(w.x, MAGIC, 0x4342));
-                    mma_top(sacc[j][b][0], sacc[j][b][1], qa[b][1][0], qa[b][1][1], __byte_perm(w.y, MAGIC, 0x4140),
-                            __byte_perm(w.y, MAGIC, 0x4342));
-                }
-            }
-
-            // ---- scores for this lane's 4 tokens: (j, e) -> token r0 + 8j + 2*t4 + e --------------
-            float s2[2][2];
-            float mx = -INFINITY;
-#pragma unroll
-            for (int j = 0; j < 2; j++) {
-#pragma unroll
-                for (int e = 0; e < 2; e++) {
-                    const int tok = r0 + 8 * j + 2 * t4 + e;
-                    const uint2 sw = *reinterpret_cast<const uint2*>(sm.ks[st] + tok * 16 + (kvh & 1) * 8);
-                    const float2 s01 = __half22float2(*reinterpret_cast<const __half2*>(&sw.x));
-                    const float2 s23 = __half22float2(*reinterpret_cast<const __half2*>(&sw.y));
-                    float s = s01.x * sacc[j][0][e];
-                    s = fmaf(s01.y, sacc[j][1][e], s);
-                    s = fmaf(s23.x, sacc[j][2][e], s);
-                    s = fmaf(s23.y, sacc[j][3][e], s);
-                    const int64_t T = (int64_t)tile_tok0 + 8 * j + 2 * t4 + e;
-                    const bool vis = T >= (int64_t)t_begin && T < (int64_t)t_end && T <= vis_last;
-                    s2[j][e] = vis ? s * scale2 : -INFINITY;
-                    mx = fmaxf(mx, s2[j][e]);
-                }
-            }
-            mx = quad_max(mx);
-            const bool grow = mx > m_run + RESCALE_T;
-            if (__any_sync(0xffffffffu, grow)) {
-                const float m_new = grow ? mx : m_run;
-                const float corr = ex2(m_run - m_new);
-                m_run = m_new;
-                l_part *= corr;
-#pragma unroll
-                for (int b = 0; b < 4; b++) {
-                    osum[b] *= corr;
-#pragma unroll
-                    for (int i = 0; i < 4; i++) {
-                        o[b][i][0] *= corr;
-                        o[b][i][1] *= corr;
-                    }
-                }
-            }
-            float p[2][2];
-#pragma unroll
-            for (int j = 0; j < 2; j++) {
-#pragma unroll
-                for (int e = 0; e < 2; e++) {
-                    p[j][e] = ex2(s2[j][e] - m_run);
-                    l_part += p[j][e];
-                }
-            }
-
-            // ---- O += P' V with P'_b = P * s_b(V): A rows = query rows, k = this tile's 16 tokens ---
-            float sv[2][2][4];
-#pragma unroll
-            for (int j = 0; j < 2; j++) {
-#pragma unroll
-                for (int e = 0; e < 2; e++) {
-                    const int tok = r0 + 8 * j + 2 * t4 + e;
-                    const uint2 sw = *reinterpret_cast<const uint2*>(sm.vs[st] + tok * 16 + (kvh & 1) * 8);
-                    const float2 s01 = __half22float2(*reinterpret_cast<const __half2*>(&sw.x));
-                    const float2 s23 = __half22float2(*reinterpret_cast<const __half2*>(&sw.y));
-                    sv[j][e][0] = s01.x;
-                    sv[j][e][1] = s01.y;
-                    sv[j][e][2] = s23.x;
-                    sv[j][e][3] = s23.y;
-                }
-            }
-            const uint8_t* vbase = sm.vq[st];
-#pragma unroll
-            for (int b = 0; b < 4; b++) {
-                const uint32_t pa0 = pack_half2(p[0][0] * sv[0][0][b], p[0][1] * sv[0][1][b]);
-                const uint32_t pa2 = pack_half2(p[1][0] * sv[1][0][b], p[1][1] * sv[1][1][b]);
-                uint32_t w[2][2];
-#pragma unroll
-                for (int j = 0; j < 2; j++) {
-#pragma unroll
-                    for (int e = 0; e < 2; e++) {
-                        const int row = r0 + 8 * j + 2 * t4 + e;
-                        const int c16 = (2 * b + (g >> 2)) ^ (row & 7);
-                        w[j][e] = *reinterpret_cast<const uint32_t*>(vbase + row * 128 + c16 * 16 + (g & 3) * 4) ^ 0x80808080u;
-                    }
-                }
-                // pair the two tokens of a k-slot byte by byte, then widen to f16
-                const uint32_t lo0 = __byte_perm(w[0][0], w[0][1], 0x5140), hi0 = __byte_perm(w[0][0], w[0][1], 0x7362);
-                const uint32_t lo1 = __byte_perm(w[1][0], w[1][1], 0x5140), hi1 = __byte_perm(w[1][0], w[1][1], 0x7362);
-                mma_top(o[b][0][0], o[b][0][1], pa0, pa2, __byte_perm(lo0, MAGIC, 0x4140), __byte_perm(lo1, MAGIC, 0x4140));
-                mma_top(o[b][1][0], o[b][1][1], pa0, pa2, __byte_perm(lo0, MAGIC, 0x4342), __byte_perm(lo1, MAGIC, 0x4342));
-                mma_top(o[b][2][0], o[b][2][1], pa0, pa2, __byte_perm(hi0, MAGIC, 0x4140), __byte_perm(hi1, MAGIC, 0x4140));
-                mma_top(o[b][3][0], o[b][3][1], pa0, pa2, __byte_perm(hi0, MAGIC, 0x4342), __byte_perm(hi1, MAGIC, 0x4342));
-                float ones_c1 = 0.0f;  // every column of P' x ones is the row sum; keep column 2*t4 only
-                mma_top(osum[b], ones_c1, pa0, pa2, 0x3C003C00u, 0x3C003C00u);
-            }
-
-            __syncwarp();
-            if (lane == 0) mbar_arrive(&sm.empty[st]);
-        }
-
-        // ---- this warp's (acc, m, l) into shared memory ---------------------------------------
-        const float l_row = quad_sum(l_part);
-        if (g < MAX_ROWS) {
-            float* dst = sm.merge[warp][g];
-#pragma unroll
-            for (int b = 0; b < 4; b++) {
-                const float corr = OFFSET * osum[b];
-#pragma unroll
-                for (int i = 0; i < 4; i++) {
-                    dst[32 * b + 8 * t4 + i] = o[b][i][0] - corr;
-                    dst[32 * b + 8 * t4 + 4 + i] = o[b][i][1] - corr;
-                }
-            }
-            if (t4 == 0) {
-                dst[HD] = m_run == NEG_SENTINEL ? NEG_SENTINEL : m_run * 0.6931471805599453f;  // back to natural log
-                dst[HD + 1] = l_row;
-            }
+        return pp;
+    };
+    // Lane 0 only: start the four TMA copies of iteration `it` into slot it % NSTAGES.
+    auto issue = [&](uint32_t it, uint32_t pp) {
+        const int st = it % NSTAGES;
+        const uint32_t tok0 = (s_begin + it) * STAGE_TOK;
+        const int row = (int)(pp * page + tok0 % page);
+        uint64_t* bar = &sm.full[warp][st];
+        fence_proxy_async_smem();  // the slot's previous contents were read through the generic proxy
+        mbar_arrive_expect_tx(bar, STAGE_BYTES);
+        tma_load_3d(sm.kq[warp][st], &tm_kq, bar, 0, kvh, row);
+        tma_load_2d(sm.ks[warp][st], &tm_ks, bar, (kvh >> 1) * 8, row);
+        tma_load_3d(sm.vq[warp][st], &tm_vq, bar, 0, kvh, row);
+        tma_load_2d(sm.vs[warp][st], &tm_vs, bar, (kvh >> 1) * 8, row);
+    };
+    {
+        const uint32_t n_pre = min(n_iter, (uint32_t)NSTAGES);
+        for (uint32_t it = 0; it < n_pre; ++it) {
+            const uint32_t pp = lookup(s_begin + it);
+            if (lane == 0) issue(it, pp);
         }
     }
-    __syncthreads();
+    // The page of the next stage to be issued is looked up one iteration early, so the load's
+    // latency is covered by a tile of work.
+    uint32_t next_pp = n_iter > (uint32_t)NSTAGES ? lookup(s_begin + NSTAGES) : 0;
 
-    // ---- merge the four warps in fixed order and write the split's partial --------------------------
-    if (threadIdx.x < CONSUMER_WARPS * 32) {
-        const int row = threadIdx.x >> 4, d0 = (threadIdx.x & 15) * 8;
-        if ((uint32_t)row < m_q * G) {
-            float m_all = NEG_SENTINEL;
+    const int g = lane >> 2, t4 = lane & 3;
+    const uint32_t rows = m_q * G;
+
+    // MMA roles.  QK^T: A = K (16 tokens x 16 dims of chunk c), B = Q^T (16 dims x 8 query rows).
+    //            PV  : A = V^T (16 dims of chunk c x 16 tokens), B = P'^T (16 tokens x 8 query rows).
+    // A lane therefore supplies Q for query row g (B operand) and owns the accumulator columns of
+    // query rows 2*t4 and 2*t4 + 1 (C operand).
+    //
+    // Q as B fragments: ldmatrix hands lane t4 the bytes 4*t4 .. 4*t4+3 of every 16-byte chunk of a K
+    // row, so k-step c contracts dims 16c + 4*t4 + {0,1 | 2,3}.
+    uint32_t qb[8][2];
+    float cinit[4][2];  // -1152 * (sum of q over block b) for query rows 2*t4 + e
+    {
+        const bool q_live = (uint32_t)g < rows;
+        const __half* qrow = q + ((size_t)(g / G) * n_q + kvh * G + g % G) * HD;
 #pragma unroll
-            for (int w = 0; w < CONSUMER_WARPS; w++) m_all = fmaxf(m_all, sm.merge[w][row][HD]);
-            float acc[8], l = 0.0f;
+        for (int b = 0; b < 4; b++) {
+            float sum = 0.0f;
 #pragma unroll
-            for (int d = 0; d < 8; d++) acc[d] = 0.0f;
-#pragma unroll
-            for (int w = 0; w < CONSUMER_WARPS; w++) {
-                const float f = __expf(sm.merge[w][row][HD] - m_all);
-                l = fmaf(f, sm.merge[w][row][HD + 1], l);
-#pragma unroll
-                for (int d = 0; d < 8; d++) acc[d] = fmaf(f, sm.merge[w][row][d0 + d], acc[d]);
+            for (int cc = 0; cc < 2; cc++) {
+                const int c = 2 * b + cc;
+                uint2 w = make_uint2(0u, 0u);
+                if (q_live) w = __ldg(reinterpret_cast<const uint2*>(qrow + 16 * c + 4 * t4));
+                qb[c][0] = w.x;
+                qb[c][1] = w.y;
+                const float2 f0 = __half22float2(*reinterpret_cast<const __half2*>(&w.x));
+                const float2 f1 = __half22float2(*reinterpret_cast<const __half2*>(&w.y));
+                sum += (f0.x + f0.y) + (f1.x + f1.y);
             }
-            const uint32_t qi = (uint32_t)row / G;
-            const int qh = kvh * G + row % G;
-            float* dst = part + (((size_t)qi * n_q + qh) * n_splits + split) * (HD + 2);
+            sum = -OFFSET * quad_sum(sum);  // now the block sum of query row g, in all 4 lanes of the quad
+            cinit[b][0] = __shfl_sync(0xffffffffu, sum, (2 * t4) * 4);
+            cinit[b][1] = __shfl_sync(0xffffffffu, sum, (2 * t4 + 1) * 4);
+        }
+    }
+    // Keys query row 2*t4 + e may see: [t_begin, hi_row[e]], hi = min(t_end - 1, kv_len - m_q + token index).
+    int hi_row[2];
 #pragma unroll
-            for (int d = 0; d < 8; d++) dst[d0 + d] = acc[d];
-            if (d0 == 0) {
-                dst[HD] = m_all;
-                dst[HD + 1] = l;
+    for (int e = 0; e < 2; e++) hi_row[e] = min((int)t_end - 1, (int)kv_len - (int)m_q + (2 * t4 + e) / G);
+    const int hi_all = min((int)t_end - 1, (int)kv_len - (int)m_q);  // visible to every row
+
+    // Per-lane shared-memory offsets (bytes) inside a head tile [16 tokens][128 B, swizzled].  For both
+    // K (plain) and V (transposed) one ldmatrix.x4 fetches block b: lane l addresses row (l & 7) of
+    // matrix (l >> 3) = (token half (l >> 3) & 1, 16-byte chunk 2b + (l >> 4)).
+    const uint32_t lrow = lane & 7, lmat = lane >> 3;
+    uint32_t off[4];
+#pragma unroll
+    for (int b = 0; b < 4; b++) off[b] = (8 * (lmat & 1) + lrow) * 128 + (((2 * b + (lmat >> 1)) ^ lrow) << 4);
+    // scales: [token][2 heads][4 f16].  K side: tokens g and g + 8; V side: tokens 2*t4 + e and 8 + 2*t4 + e.
+    const uint32_t ksc_off = g * 16 + (kvh & 1) * 8;
+    const uint32_t vsc_off = (2 * t4) * 16 + (kvh & 1) * 8;
+
+    const float scale2 = scale * 1.4426950408889634f;
+    float m_run[2] = {NEG_SENTINEL, NEG_SENTINEL}, l_part[2] = {0.0f, 0.0f};
+    float o[8][4];     // o[c]: dims 16c + 2g (c0, c1) and 16c + 2g + 1 (c2, c3) x query rows 2*t4 (c0, c2), 2*t4 + 1 (c1, c3)
+    float osum[4][4];  // per block: sum over tokens of P'_b, same column layout
+#pragma unroll
+    for (int c = 0; c < 8; c++) o[c][0] = o[c][1] = o[c][2] = o[c][3] = 0.0f;
+#pragma unroll
+    for (int b = 0; b < 4; b++) osum[b][0] = osum[b][1] = osum[b][2] = osum[b][3] = 0.0f;
+    const uint32_t ones[4] = {0x3C003C00u, 0x3C003C00u, 0x3C003C00u, 0x3C003C00u};
+
+    bool failed = false;
+    for (uint32_t it = 0; it < n_iter; ++it) {
+        const int st = it % NSTAGES;
+        mbar_wait(&sm.full[warp][st], (it / NSTAGES) & 1, status, 305, failed);
+        const int tok0 = (int)((s_begin + it) * STAGE_TOK);
+        const uint32_t kq_base = smem_u32(sm.kq[warp][st]), vq_base = smem_u32(sm.vq[warp][st]);
+
+        // ---- S = K Q^T per 32-wide block, then the block scales: s[th][e] = score of token g + 8*th
+        //      against query row 2*t4 + e -----------------------------------------------------------
+        float s[2][2];
+        {
+            const uint2 sa = lds_u2(smem_u32(sm.ks[warp][st]) + ksc_off);        // scales of token g
+            const uint2 sb = lds_u2(smem_u32(sm.ks[warp][st]) + ksc_off + 128);  // scales of token g + 8
+            const float2 a01 = __half22float2(*reinterpret_cast<const __half2*>(&sa.x));
+            const float2 a23 = __half22float2(*reinterpret_cast<const __half2*>(&sa.y));
+            const float2 b01 = __half22float2(*reinterpret_cast<const __half2*>(&sb.x));
+            const float2 b23 = __half22float2(*reinterpret_cast<const __half2*>(&sb.y));
+            const float ka[4] = {a01.x, a01.y, a23.x, a23.y}, kb[4] = {b01.x, b01.y, b23.x, b23.y};
+            s[0][0] = s[0][1] = s[1][0] = s[1][1] = 0.0f;
+#pragma unroll
+            for (int b = 0; b < 4; b++) {
+                uint32_t x[4];  // (token half 0, chunk 2b), (1, 2b), (0, 2b+1), (1, 2b+1): bytes 4*t4.. of token g (+8)
+                ldsm_x4(kq_base + off[b], x);
+                float acc[4] = {cinit[b][0], cinit[b][1], cinit[b][0], cinit[b][1]};
+#pragma unroll
+                for (int cc = 0; cc < 2; cc++) {
+                    const uint32_t x0 = x[2 * cc] ^ 0x80808080u, x1 = x[2 * cc + 1] ^ 0x80808080u;
+                    const uint32_t a[4] = {__byte_perm(x0, MAGIC, 0x4140), __byte_perm(x1, MAGIC, 0x4140),
+                                           __byte_perm(x0, MAGIC, 0x4342), __byte_perm(x1, MAGIC, 0x4342)};
+                    mma16816(acc, a, qb[2 * b + cc][0], qb[2 * b + cc][1]);
+                }
+                s[0][0] = fmaf(ka[b], acc[0], s[0][0]);
+                s[0][1] = fmaf(ka[b], acc[1], s[0][1]);
+                s[1][0] = fmaf(kb[b], acc[2], s[1][0]);
+                s[1][1] = fmaf(kb[b], acc[3], s[1][1]);
+            }
+        }
+#pragma unroll
+        for (int th = 0; th < 2; th++) {
+            s[th][0] *= scale2;
+            s[th][1] *= scale2;
+        }
+        // Masks only on the stages that straddle the split's ends or the causal edge of the draft.
+        if (tok0 < (int)t_begin || tok0 + STAGE_TOK - 1 > hi_all) {
+#pragma unroll
+            for (int th = 0; th < 2; th++) {
+                const int T = tok0 + g + 8 * th;
+#pragma unroll
+                for (int e = 0; e < 2; e++)
+                    if (T < (int)t_begin || T > hi_row[e]) s[th][e] = -INFINITY;
+            }
+        }
+        const float mx0 = tok_max(fmaxf(s[0][0], s[1][0])), mx1 = tok_max(fmaxf(s[0][1], s[1][1]));
+        const bool grow0 = mx0 > m_run[0] + RESCALE_T, grow1 = mx1 > m_run[1] + RESCALE_T;
+        if (__any_sync(0xffffffffu, grow0 || grow1)) {
+            const float n0 = grow0 ? mx0 : m_run[0], n1 = grow1 ? mx1 : m_run[1];
+            const float c0 = ex2(m_run[0] - n0), c1 = ex2(m_run[1] - n1);
+            m_run[0] = n0;
+            m_run[1] = n1;
+            l_part[0] *= c0;
+            l_part[1] *= c1;
+#pragma unroll
+            for (int c = 0; c < 8; c++) {
+                o[c][0] *= c0;
+                o[c][1] *= c1;
+                o[c][2] *= c0;
+                o[c][3] *= c1;
+            }
+#pragma unroll
+            for (int b = 0; b < 4; b++) {
+                osum[b][0] *= c0;
+                osum[b][1] *= c1;
+                osum[b][2] *= c0;
+                osum[b][3] *= c1;
+            }
+        }
+        const float p00 = ex2(s[0][0] - m_run[0]), p01 = ex2(s[0][1] - m_run[1]);
+        const float p10 = ex2(s[1][0] - m_run[0]), p11 = ex2(s[1][1] - m_run[1]);
+        l_part[0] += p00 + p10;
+        l_part[1] += p01 + p11;
+
+        // ---- P (tokens x query rows) -> P^T fragments: lane (g, t4) gets query row g, tokens 2*t4, 2*t4+1
+        //      (and 8 + those); then P'_b = P * (V scale of block b), and O^T += V^T P'^T ----------------
+        const uint32_t pt0 = movmatrix_trans(pack_half2(p00, p01));
+        const uint32_t pt1 = movmatrix_trans(pack_half2(p10, p11));
+        const uint32_t vs_base = smem_u32(sm.vs[warp][st]) + vsc_off;
+        const uint2 va = lds_u2(vs_base), vb = lds_u2(vs_base + 16);              // tokens 2*t4, 2*t4+1
+        const uint2 vc = lds_u2(vs_base + 8 * 16), vd = lds_u2(vs_base + 9 * 16);  // tokens 8+2*t4, 9+2*t4
+#pragma unroll
+        for (int b = 0; b < 4; b++) {
+            // (scale_b of token A, scale_b of token B) as a half2, times (p_A, p_B)
+            const uint32_t sel = (b & 1) ? 0x7632u : 0x5410u;
+            const uint32_t pb0 = hmul2_u32(pt0, __byte_perm(b < 2 ? va.x : va.y, b < 2 ? vb.x : vb.y, sel));
+            const uint32_t pb1 = hmul2_u32(pt1, __byte_perm(b < 2 ? vc.x : vc.y, b < 2 ? vd.x : vd.y, sel));
+            uint32_t y[4];  // transposed: bytes V[8th + 2*t4 (+1)][16c + 2g (+1)] for (th, c) = (0,2b),(1,2b),(0,2b+1),(1,2b+1)
+            ldsm_x4_trans(vq_base + off[b], y);
+#pragma unroll
+            for (int cc = 0; cc < 2; cc++) {
+                const uint32_t y0 = y[2 * cc] ^ 0x80808080u, y1 = y[2 * cc + 1] ^ 0x80808080u;
+                const uint32_t a[4] = {__byte_perm(y0, MAGIC, 0x4240), __byte_perm(y0, MAGIC, 0x4341),
+                                       __byte_perm(y1, MAGIC, 0x4240), __byte_perm(y1, MAGIC, 0x4341)};
+                mma16816(o[2 * b + cc], a, pb0, pb1);
+            }
+            mma16816(osum[b], ones, pb0, pb1);
+        }
+
+        // Refill this slot for iteration it + NSTAGES; every lane is done reading it.
+        __syncwarp();
+        if (it + NSTAGES < n_iter) {
+            if (lane == 0) issue(it + NSTAGES, next_pp);
+            if (it + NSTAGES + 1 < n_iter) next_pp = lookup(s_begin + it + NSTAGES + 1);
+        }
+    }
+
+    // ---- this head's partial for the split, straight from registers ----------------------------------
+#pragma unroll
+    for (int e = 0; e < 2; e++) {
+        const uint32_t r = 2 * t4 + e;  // query row = token index * G + head within the group
+        const float l_row = tok_sum(l_part[e]);
+        if (r < rows) {
+            float* dst = part + (((size_t)(r / G) * n_q + kvh * G + r % G) * n_splits + split) * (HD + 2);
+#pragma unroll
+            for (int c = 0; c < 8; c++) {
+                const float corr = OFFSET * osum[c >> 1][e];
+                // dims 16c + 2g and 16c + 2g + 1; rows are 520 bytes, so 8-byte aligned stores
+                *reinterpret_cast<float2*>(dst + 16 * c + 2 * g) = make_float2(o[c][e] - corr, o[c][2 + e] - corr);
+            }
+            if (g == 0) {
+                dst[HD] = m_run[e] == NEG_SENTINEL ? NEG_SENTINEL : m_run[e] * 0.6931471805599453f;  // back to natural log
+                dst[HD + 1] = l_row;
             }
         }
     }
@@ -379,37 +387,64 @@ struct PushDecodePaged {
     uint32_t page;
 };
 
+// Tensor maps of the four pools: quants as [row][kv head][128] u8 with a (128, 1, 16) box and the
+// 128-byte swizzle, scales as [row][kv heads * 4] f16 with a (hpc * 4, 16) box.
+int encode_pool_maps(const LaunchArgs& a, CUtensorMap (&tm)[4], const void* const (&quants)[2], const void* const (&scales)[2],
+                     uint32_t n_kv, uint64_t pool_rows)
+{
+    for (int i = 0; i < 2; i++) {
+        const uint64_t qd[3] = {HD, n_kv, pool_rows};
+        const uint64_t qs[2] = {HD, (uint64_t)n_kv * HD};
+        const uint32_t qb[3] = {HD, 1, STAGE_TOK};
+        if (int r = encode_tensor_map(a, &tm[2 * i], 0, 3, const_cast<void*>(quants[i]), qd, qs, qb, 3)) return r;
+        const uint64_t sd[2] = {(uint64_t)n_kv * 4, pool_rows};
+        const uint64_t ss[1] = {(uint64_t)n_kv * 8};
+        const uint32_t sb[2] = {8, STAGE_TOK};
+        if (int r = encode_tensor_map(a, &tm[2 * i + 1], 1, 2, const_cast<void*>(scales[i]), sd, ss, sb, 0)) return r;
+    }
+    return 0;
+}
+
 template <int NSTAGES, int MIN_CTAS>
-int launch_variant(const LaunchArgs& a, const CUtensorMap (&tm)[4], const PushDecodePaged& p, int n_kv, uint32_t m_q,
-                   size_t pool_rows)
+cudaError_t launch_decode_variant(cudaStream_t stream, int device, const CUtensorMap (&tm)[4], const __half* q,
+                                  const uint32_t* page_table, uint32_t table_len, uint32_t page, uint32_t pool_pages, float* part,
+                                  const uint32_t* step, uint32_t n_kv, uint32_t n_splits, float scale, uint32_t m_q, uint32_t* status)
 {
     using Smem = DecodeSmem<NSTAGES>;
     const size_t smem = sizeof(Smem) + 1024;
     static bool attr_set[64] = {};
-    if (a.device < 64 && !attr_set[a.device]) {
-        if (int r = check_cuda(a, cudaFuncSetAttribute(decode_paged_kernel<NSTAGES, MIN_CTAS>,
-                                                       cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem),
-                               "cudaFuncSetAttribute(decode_paged)"))
-            return r;
-        attr_set[a.device] = true;
+    if (device >= 0 && device < 64 && !attr_set[device]) {
+        cudaError_t e = cudaFuncSetAttribute(decode_paged_kernel<NSTAGES, MIN_CTAS>, cudaFuncAttributeMaxDynamicSharedMemorySize,
+                                             (int)smem);
+        if (e != cudaSuccess) return e;
+        attr_set[device] = true;
     }
-    decode_paged_kernel<NSTAGES, MIN_CTAS><<<dim3(n_kv, p.n_splits), THREADS, smem, a.stream>>>(
-        tm[0], tm[1], tm[2], tm[3], (const __half*)a.b[0].ptr, (const uint32_t*)a.b[5].ptr, (uint32_t)(a.b[5].bytes / 4), p.page,
-        (uint32_t)(pool_rows / p.page), (float*)a.b[6].ptr, (const uint32_t*)a.b[7].ptr, p.n_splits, p.scale, m_q, a.status);
-    ++*a.launches;
-    return check_cuda(a, cudaGetLastError(), "attn_decode_paged_q8kv_d128");
+    decode_paged_kernel<NSTAGES, MIN_CTAS><<<dim3((n_kv + WPC - 1) / WPC, n_splits), WPC * 32, smem, stream>>>(
+        tm[0], tm[1], tm[2], tm[3], q, page_table, table_len, page, pool_pages, part, step, n_kv, n_splits, scale, m_q, status);
+    return cudaGetLastError();
 }
 
-// Pipeline shape: 3 stages x 18 KB + the merge buffer = 72 KB, three CTAs per SM (default), or
-// 4 stages and two CTAs per SM with more registers per thread.  SGB_DECODE_PIPELINE=4x2 picks the
-// second; it exists for tuning and changes no result bit.
+// Pipeline shape.  Default: 4 stages of 4.5 KB per warp = 72 KB per CTA, three CTAs (12 warps) per
+// SM at up to 168 registers.  SGB_DECODE_PIPELINE=3x4 selects three stages and four CTAs (16 warps)
+// per SM at 128 registers; it exists for tuning and changes no result bit.
 int pipeline_choice()
 {
     static int choice = [] {
         const char* e = getenv("SGB_DECODE_PIPELINE");
-        return (e && e[0] == '4') ? 1 : 0;
+        return (e && e[0] == '3') ? 1 : 0;
     }();
     return choice;
+}
+
+cudaError_t launch_decode(cudaStream_t stream, int device, const CUtensorMap (&tm)[4], const __half* q, const uint32_t* page_table,
+                          uint32_t table_len, uint32_t page, uint32_t pool_pages, float* part, const uint32_t* step, uint32_t n_kv,
+                          uint32_t n_splits, float scale, uint32_t m_q, uint32_t* status)
+{
+    if (pipeline_choice())
+        return launch_decode_variant<3, 4>(stream, device, tm, q, page_table, table_len, page, pool_pages, part, step, n_kv, n_splits,
+                                           scale, m_q, status);
+    return launch_decode_variant<4, 3>(stream, device, tm, q, page_table, table_len, page, pool_pages, part, step, n_kv, n_splits,
+                                       scale, m_q, status);
 }
 
 }  // namespace
@@ -421,13 +456,13 @@ int pipeline_choice()
 int launch_decode_paged_q8kv_d128(const LaunchArgs& a)
 {
     const PushDecodePaged p = *(const PushDecodePaged*)a.push;
-    const int n_kv = (int)a.groups[0];
+    const uint32_t n_kv = a.groups[0];
     const uint32_t m_q = a.groups[2] ? a.groups[2] : 1;
-    if (n_kv <= 0 || (n_kv & 1)) return fail_validation(a, "decode_paged: groups[0] (kv heads) must be even and > 0");
+    if (n_kv == 0 || (n_kv & 1)) return fail_validation(a, "decode_paged: groups[0] (kv heads) must be even and > 0");
     if (p.n_splits == 0 || a.groups[1] != p.n_splits)
         return fail_validation(a, "decode_paged: groups[1] must equal push.n_splits (> 0)");
     if (m_q > 4) return fail_validation(a, "decode_paged: at most 4 query tokens");
-    if (p.page == 0 || p.page % STAGE_TOK) return fail_validation(a, "decode_paged: page must be a multiple of 64 tokens");
+    if (p.page == 0 || p.page % STAGE_TOK) return fail_validation(a, "decode_paged: page must be a multiple of 16 tokens");
     const size_t row_bytes = (size_t)n_kv * HD;
     const size_t pool_rows = a.b[1].bytes / row_bytes;
     if (pool_rows == 0 || a.b[3].bytes / row_bytes != pool_rows)
@@ -443,19 +478,14 @@ int launch_decode_paged_q8kv_d128(const LaunchArgs& a)
         if (reinterpret_cast<uintptr_t>(a.b[i].ptr) & 15) return fail_validation(a, "decode_paged: K/V pools must be 16-byte aligned");
 
     CUtensorMap tm[4];
-    for (int i = 0; i < 2; i++) {
-        const uint64_t qd[3] = {HD, (uint64_t)n_kv, pool_rows};
-        const uint64_t qs[2] = {HD, row_bytes};
-        const uint32_t qb[3] = {HD, 1, STAGE_TOK};
-        if (int r = encode_tensor_map(a, &tm[2 * i], 0, 3, a.b[1 + 2 * i].ptr, qd, qs, qb, 3)) return r;
-        const uint64_t sd[2] = {(uint64_t)n_kv * 4, pool_rows};
-        const uint64_t ss[1] = {(uint64_t)n_kv * 8};
-        const uint32_t sb[2] = {8, STAGE_TOK};
-        if (int r = encode_tensor_map(a, &tm[2 * i + 1], 1, 2, a.b[2 + 2 * i].ptr, sd, ss, sb, 0)) return r;
-    }
-
-    return pipeline_choice() ? launch_variant<4, 2>(a, tm, p, n_kv, m_q, pool_rows)
-                             : launch_variant<3, 3>(a, tm, p, n_kv, m_q, pool_rows);
+    const void* const quants[2] = {a.b[1].ptr, a.b[3].ptr};
+    const void* const scales[2] = {a.b[2].ptr, a.b[4].ptr};
+    if (int r = encode_pool_maps(a, tm, quants, scales, n_kv, pool_rows)) return r;
+    const cudaError_t e = launch_decode(a.stream, a.device, tm, (const __half*)a.b[0].ptr, (const uint32_t*)a.b[5].ptr,
+                                        (uint32_t)(a.b[5].bytes / 4), p.page, (uint32_t)(pool_rows / p.page), (float*)a.b[6].ptr,
+                                        (const uint32_t*)a.b[7].ptr, n_kv, p.n_splits, p.scale, m_q, a.status);
+    ++*a.launches;
+    return check_cuda(a, e, "attn_decode_paged_q8kv_d128");
 }
 
 }  // namespace sgb
@@ -528,7 +558,7 @@ extern "C" int sgb_decode_paged_q8kv_d128_noalloc(int device, void* stream, cons
     if (n_kv_heads == 0 || (n_kv_heads & 1)) return set_last_error(3, "decode_noalloc: n_kv_heads must be even and > 0");
     if (m_q == 0 || m_q > 4) return set_last_error(3, "decode_noalloc: m_q must be 1..4");
     if (kv_len == 0 || n_splits == 0) return set_last_error(3, "decode_noalloc: kv_len and n_splits must be > 0");
-    if (page == 0 || page % STAGE_TOK) return set_last_error(3, "decode_noalloc: page must be a multiple of 64 tokens");
+    if (page == 0 || page % STAGE_TOK) return set_last_error(3, "decode_noalloc: page must be a multiple of 16 tokens");
     const uint64_t part_rows = (uint64_t)m_q * n_kv_heads * G * n_splits;
     if (part_rows > NOALLOC_MAX_PART_ROWS) {
         char buf[200];
@@ -556,16 +586,13 @@ extern "C" int sgb_decode_paged_q8kv_d128_noalloc(int device, void* stream, cons
     } restore{prev, device};
 
     // Set-up on the first call per device, with that device current: resolve the device address of
-    // the static array and raise the kernel's shared-memory limit.  Neither allocates.
+    // the static array (the decode launcher raises its kernel's shared-memory limit on its own first
+    // use per device).  Neither allocates.
     if (!g_noalloc_ready[device]) {
         void* ptr = nullptr;
         e = cudaGetSymbolAddress(&ptr, g_noalloc_scratch);
         if (e != cudaSuccess || ptr == nullptr)
             return set_last_error(4, std::string("decode_noalloc: cudaGetSymbolAddress: ") + cudaGetErrorString(e));
-        e = cudaFuncSetAttribute(decode_paged_kernel<4, 2>, cudaFuncAttributeMaxDynamicSharedMemorySize,
-                                 (int)(sizeof(DecodeSmem<4>) + 1024));
-        if (e != cudaSuccess)
-            return set_last_error(4, std::string("decode_noalloc: cudaFuncSetAttribute: ") + cudaGetErrorString(e));
         g_noalloc_dev_ptr[device] = ptr;
         g_noalloc_ready[device] = true;
     }
@@ -575,25 +602,15 @@ extern "C" int sgb_decode_paged_q8kv_d128_noalloc(int device, void* stream, cons
     std::string err;
     uint64_t launches = 0;
     LaunchArgs a{(cudaStream_t)stream, nullptr, nullptr, {n_kv_heads, n_splits, m_q}, status, 0, device, &err, &launches};
-    const size_t row_bytes = (size_t)n_kv_heads * HD;
     CUtensorMap tm[4];
-    const void* quants[2] = {k_quants, v_quants};
-    const void* scales[2] = {k_scales, v_scales};
-    for (int i = 0; i < 2; i++) {
-        const uint64_t qd[3] = {HD, n_kv_heads, pool_rows};
-        const uint64_t qs[2] = {HD, row_bytes};
-        const uint32_t qb[3] = {HD, 1, STAGE_TOK};
-        if (int r = encode_tensor_map(a, &tm[2 * i], 0, 3, const_cast<void*>(quants[i]), qd, qs, qb, 3)) return set_last_error(r, err);
-        const uint64_t sd[2] = {(uint64_t)n_kv_heads * 4, pool_rows};
-        const uint64_t ss[1] = {(uint64_t)n_kv_heads * 8};
-        const uint32_t sb[2] = {8, STAGE_TOK};
-        if (int r = encode_tensor_map(a, &tm[2 * i + 1], 1, 2, const_cast<void*>(scales[i]), sd, ss, sb, 0)) return set_last_error(r, err);
-    }
+    const void* const quants[2] = {k_quants, v_quants};
+    const void* const scales[2] = {k_scales, v_scales};
+    if (int r = encode_pool_maps(a, tm, quants, scales, n_kv_heads, pool_rows)) return set_last_error(r, err);
     cudaStream_t s = (cudaStream_t)stream;
     noalloc_step_kernel<<<1, 1, 0, s>>>(kv_len);
-    decode_paged_kernel<4, 2><<<dim3(n_kv_heads, n_splits), THREADS, sizeof(DecodeSmem<4>) + 1024, s>>>(
-        tm[0], tm[1], tm[2], tm[3], (const __half*)q, page_table, table_len, page, (uint32_t)(pool_rows / page), scratch, step,
-        n_splits, scale, m_q, status);
+    e = launch_decode(s, device, tm, (const __half*)q, page_table, table_len, page, (uint32_t)(pool_rows / page), scratch, step,
+                      n_kv_heads, n_splits, scale, m_q, status);
+    if (e != cudaSuccess) return set_last_error(4, std::string("decode_noalloc: launch: ") + cudaGetErrorString(e));
     noalloc_reduce_kernel<<<m_q * n_kv_heads * G, HD, 0, s>>>(out, n_splits);
     e = cudaGetLastError();
     if (e != cudaSuccess) return set_last_error(4, std::string("decode_noalloc: launch: ") + cudaGetErrorString(e));

@@ -43,17 +43,24 @@ constexpr uint32_t TMEM_S = 0;    // S: 64 f32 columns
 constexpr uint32_t TMEM_O = 64;   // O: 128 f32 columns
 constexpr float RESCALE_T = 8.0f;
 
-struct __align__(1024) FlashSmem {
+// 112 KB of tiles + 64 B of barriers.  Two CTAs must fit in the SM's 228 KB next to the 1 KB the
+// system reserves per CTA, so the struct is NOT padded to its 1024-byte tile alignment: the dynamic
+// shared-memory base is declared 1024-aligned instead (and checked at run time).
+struct FlashSmem {
     uint8_t q[2][2 * HALF_TILE];             // [dim half][128 rows x 128 B]
     uint8_t k[KV_STAGES][2][HALF_TILE];      // [stage][dim half][64 keys x 128 B]
     uint8_t v[KV_STAGES][2][HALF_TILE];
     uint8_t p[2 * HALF_TILE];                // [128 rows x 128 B] = 64 f16 keys per row
-    uint64_t full[KV_STAGES];
+    uint64_t full_k[KV_STAGES];
+    uint64_t full_v[KV_STAGES];
     uint64_t q_bar;
     uint64_t s_bar;
     uint64_t pv_bar;
     uint32_t tmem_base;
+    uint32_t pad;
 };
+static_assert(sizeof(FlashSmem) == 7 * 2 * HALF_TILE + 64, "tiles + barriers, no padding");
+static_assert(2 * (sizeof(FlashSmem) + 1024) <= 228 * 1024, "two CTAs per SM");
 
 struct FlashParams {
     const uint32_t* step;
@@ -82,8 +89,12 @@ __global__ void __launch_bounds__(FLASH_THREADS, 2) flash_prefill_kernel(const _
                                                                          const __grid_constant__ CUtensorMap tm_v1,
                                                                          const FlashParams prm)
 {
-    extern __shared__ uint8_t smem_raw[];
-    FlashSmem& sm = *reinterpret_cast<FlashSmem*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~uintptr_t(1023));
+    extern __shared__ __align__(1024) uint8_t smem_raw[];
+    FlashSmem& sm = *reinterpret_cast<FlashSmem*>(smem_raw);
+    if ((smem_u32(smem_raw) & 1023u) != 0u) {  // the swizzled tiles need it; never seen, but never assumed
+        if (threadIdx.x == 0) report_error(prm.status, DEV_ERR_BOUNDS, 400, smem_u32(smem_raw), 0);
+        return;
+    }
 
     const int tid = threadIdx.x, warp = tid >> 5;
     const int n_qtiles = gridDim.x;
@@ -132,7 +143,10 @@ __global__ void __launch_bounds__(FLASH_THREADS, 2) flash_prefill_kernel(const _
 
     // ---- set-up -----------------------------------------------------------------------------------------
     if (tid == 0) {
-        for (int i = 0; i < KV_STAGES; i++) mbar_init(&sm.full[i], 1);
+        for (int i = 0; i < KV_STAGES; i++) {
+            mbar_init(&sm.full_k[i], 1);
+            mbar_init(&sm.full_v[i], 1);
+        }
         mbar_init(&sm.q_bar, 1);
         mbar_init(&sm.s_bar, 1);
         mbar_init(&sm.pv_bar, 1);
@@ -150,23 +164,53 @@ __global__ void __launch_bounds__(FLASH_THREADS, 2) flash_prefill_kernel(const _
     tc_fence_after_sync();
     const uint32_t tmem = sm.tmem_base;
 
-    auto load_kv = [&](int it) {
+    auto load_k = [&](int it) {
         const Tile t = tile_at(it);
         const int st = it % KV_STAGES;
         const CUtensorMap* mk = (TWO_SRC && t.src) ? &tm_k1 : &tm_k0;
+        mbar_arrive_expect_tx(&sm.full_k[st], KV_TILE_BYTES);
+        tma_load_3d(sm.k[st][0], mk, &sm.full_k[st], 0, kvh, t.row0);
+        tma_load_3d(sm.k[st][1], mk, &sm.full_k[st], 64, kvh, t.row0);
+    };
+    auto load_v = [&](int it) {
+        const Tile t = tile_at(it);
+        const int st = it % KV_STAGES;
         const CUtensorMap* mv = (TWO_SRC && t.src) ? &tm_v1 : &tm_v0;
-        mbar_arrive_expect_tx(&sm.full[st], 2 * KV_TILE_BYTES);
-        tma_load_3d(sm.k[st][0], mk, &sm.full[st], 0, kvh, t.row0);
-        tma_load_3d(sm.k[st][1], mk, &sm.full[st], 64, kvh, t.row0);
-        tma_load_3d(sm.v[st][0], mv, &sm.full[st], 0, kvh, t.row0);
-        tma_load_3d(sm.v[st][1], mv, &sm.full[st], 64, kvh, t.row0);
+        mbar_arrive_expect_tx(&sm.full_v[st], KV_TILE_BYTES);
+        tma_load_3d(sm.v[st][0], mv, &sm.full_v[st], 0, kvh, t.row0);
+        tma_load_3d(sm.v[st][1], mv, &sm.full_v[st], 64, kvh, t.row0);
+    };
+    constexpr uint32_t IDESC_QK = umma_idesc_f16(BLOCK_M, BLOCK_N, 0, 0);
+    constexpr uint32_t IDESC_PV = umma_idesc_f16(BLOCK_M, HD, 0, 1);
+    bool failed = false;
+    // S = Q K^T for tile `it` (8 MMAs of K = 16), issued by thread 0 once K(it) has landed.
+    auto issue_qk = [&](int it) {
+        const int st = it % KV_STAGES;
+        mbar_wait(&sm.full_k[st], (it / KV_STAGES) & 1, prm.status, 402, failed);
+        tc_fence_after_sync();
+#pragma unroll
+        for (int h = 0; h < 2; h++) {
+#pragma unroll
+            for (int j = 0; j < 4; j++) {
+                const uint64_t da = umma_desc_sw128(smem_u32(sm.q[h]) + j * 32, 16, 1024);
+                const uint64_t db = umma_desc_sw128(smem_u32(sm.k[st][h]) + j * 32, 16, 1024);
+                umma_f16_ss(tmem + TMEM_S, da, db, IDESC_QK, (h | j) ? 1u : 0u);
+            }
+        }
     };
 
+    // The tensor pipe runs in order, so one commit after "PV(it), QK(it+1)" tells the CTA three
+    // things at once when s_bar flips: S(it+1) is ready, P and V(it) have been consumed, O is stable.
     if (tid == 0) {
         mbar_arrive_expect_tx(&sm.q_bar, Q_BYTES);
         tma_load_3d(sm.q[0], &tm_q, &sm.q_bar, 0, kvh * G, (int)m0);
         tma_load_3d(sm.q[1], &tm_q, &sm.q_bar, 64, kvh * G, (int)m0);
-        load_kv(0);
+        load_k(0);
+        load_v(0);
+        if (n_tiles > 1) load_k(1);
+        mbar_wait(&sm.q_bar, 0, prm.status, 401, failed);
+        issue_qk(0);
+        umma_commit(&sm.s_bar);
     }
 
     // Row r of the tile <-> TMEM lane r <-> thread r: token m0 + r/2, query head kvh*2 + r%2.
@@ -176,35 +220,20 @@ __global__ void __launch_bounds__(FLASH_THREADS, 2) flash_prefill_kernel(const _
     const int64_t row_lo = (prm.window != 0 && qpos + 1 > (int64_t)prm.window) ? qpos + 1 - prm.window : 0;
     const float scale2 = prm.scale * 1.4426950408889634f;
     const uint32_t lane_addr = tmem + ((uint32_t)(warp * 32) << 16);
-    constexpr uint32_t IDESC_QK = umma_idesc_f16(BLOCK_M, BLOCK_N, 0, 0);
-    constexpr uint32_t IDESC_PV = umma_idesc_f16(BLOCK_M, HD, 0, 1);
 
     float m_run = NEG_SENTINEL, l_run = 0.0f;
-    bool failed = false;
 
     for (int it = 0; it < n_tiles; ++it) {
         const int st = it % KV_STAGES;
         const Tile t = tile_at(it);
 
-        if (tid == 0) {
-            // The other stage was last read by PV of tile it-1, which has completed (pv_bar below).
-            if (it + 1 < n_tiles) load_kv(it + 1);
-            if (it == 0) mbar_wait(&sm.q_bar, 0, prm.status, 401, failed);
-            mbar_wait(&sm.full[st], (it / KV_STAGES) & 1, prm.status, 402, failed);
-            tc_fence_after_sync();
-#pragma unroll
-            for (int h = 0; h < 2; h++) {
-#pragma unroll
-                for (int j = 0; j < 4; j++) {
-                    const uint64_t da = umma_desc_sw128(smem_u32(sm.q[h]) + j * 32, 16, 1024);
-                    const uint64_t db = umma_desc_sw128(smem_u32(sm.k[st][h]) + j * 32, 16, 1024);
-                    umma_f16_ss(tmem + TMEM_S, da, db, IDESC_QK, (h | j) ? 1u : 0u);
-                }
-            }
-            umma_commit(&sm.s_bar);
-        }
         mbar_wait(&sm.s_bar, it & 1, prm.status, 403, failed);
         tc_fence_after_sync();
+        if (tid == 0) {
+            // S(it) ready => QK(it) and PV(it-1) are done: K stage it%2 and V stage (it+1)%2 are free.
+            if (it + 1 < n_tiles) load_v(it + 1);
+            if (it + 2 < n_tiles) load_k(it + 2);
+        }
 
         // ---- softmax on this thread's row -----------------------------------------------------------
         uint32_t sv[64];
@@ -280,6 +309,7 @@ __global__ void __launch_bounds__(FLASH_THREADS, 2) flash_prefill_kernel(const _
         __syncthreads();
 
         if (tid == 0) {
+            mbar_wait(&sm.full_v[st], (it / KV_STAGES) & 1, prm.status, 405, failed);
             tc_fence_after_sync();
 #pragma unroll
             for (int j = 0; j < 4; j++) {
@@ -287,11 +317,16 @@ __global__ void __launch_bounds__(FLASH_THREADS, 2) flash_prefill_kernel(const _
                 const uint64_t db = umma_desc_sw128(smem_u32(sm.v[st][0]) + j * 2048, HALF_TILE, 1024);
                 umma_f16_ss(tmem + TMEM_O, da, db, IDESC_PV, (it | j) ? 1u : 0u);
             }
-            umma_commit(&sm.pv_bar);
+            if (it + 1 < n_tiles) {
+                issue_qk(it + 1);
+                umma_commit(&sm.s_bar);
+            } else {
+                umma_commit(&sm.pv_bar);
+            }
         }
-        mbar_wait(&sm.pv_bar, it & 1, prm.status, 404, failed);
-        tc_fence_after_sync();
     }
+    mbar_wait(&sm.pv_bar, 0, prm.status, 404, failed);
+    tc_fence_after_sync();
 
     // ---- epilogue: out = O / l.  The TMEM loads are warp-wide, so every thread takes part and only
     // the stores are predicated (rows past the end of the chunk are not written). -------------------------
@@ -365,7 +400,7 @@ int run_flash(const LaunchArgs& a, const BufView& q, const BufView& k0, const Bu
         tk1 = tk0;
         tv1 = tv0;
     }
-    const size_t smem = sizeof(FlashSmem) + 1024;
+    const size_t smem = sizeof(FlashSmem);
     static bool attr_set[2][64] = {};
     if (a.device < 64 && !attr_set[TWO_SRC][a.device]) {
         if (int r = check_cuda(a, cudaFuncSetAttribute(flash_prefill_kernel<TWO_SRC>, cudaFuncAttributeMaxDynamicSharedMemorySize,
