@@ -7,8 +7,10 @@
 // reference's; row = i * H + qh for query token i.
 //
 // Design (HBM-bound: 17/16 byte per K/V element is all that has to move):
-//   * one warp per (kv head, split), four warps (four adjacent kv heads) per CTA, so a token row is
-//     fetched as 4 x 128 adjacent bytes of quants at about the same time.  Every warp runs its own
+//   * a CTA is four warps = (4 / SUB adjacent kv heads) x (SUB sub-splits of one split); the
+//     sub-splits of a head take its 16-token stages round-robin and are merged in fixed order at
+//     the end, so the grid fills the SMs in one wave whatever n_splits the caller chose (the
+//     partials keep the reference's [row][split][130] layout).  Every warp runs its own
 //     pipeline: lane 0 issues the TMA loads of its head's 16-token stages (K quants, V quants, and
 //     the 16-byte scale pairs of its head and its neighbour) NSTAGES ahead, through the page
 //     table, into the warp's private ring of shared-memory stages; the only synchronisation is the
@@ -116,7 +118,7 @@ __device__ __forceinline__ float quad_sum(float v)
     return v + __shfl_xor_sync(0xffffffffu, v, 2);
 }
 
-template <int NSTAGES, int MIN_CTAS>
+template <int NSTAGES, int MIN_CTAS, int SUB>
 __global__ void __launch_bounds__(WPC * 32, MIN_CTAS)
     decode_paged_kernel(const __grid_constant__ CUtensorMap tm_kq, const __grid_constant__ CUtensorMap tm_ks,
                         const __grid_constant__ CUtensorMap tm_vq, const __grid_constant__ CUtensorMap tm_vs,
@@ -127,24 +129,30 @@ __global__ void __launch_bounds__(WPC * 32, MIN_CTAS)
     extern __shared__ uint8_t smem_raw[];
     using Smem = DecodeSmem<NSTAGES>;
     Smem& sm = *reinterpret_cast<Smem*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~uintptr_t(1023));
+    static_assert(NSTAGES * HEAD_TILE >= 8 * (HD + 2) * 4, "a warp's K ring doubles as its merge buffer");
 
     const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
-    const int kvh = blockIdx.x * WPC + warp, split = blockIdx.y;
+    constexpr int HEADS_PER_CTA = WPC / SUB;
+    const int kvh = blockIdx.x * HEADS_PER_CTA + warp / SUB, sub = warp % SUB, split = blockIdx.y;
     const int n_q = (int)n_kv * G;
-
-    const uint32_t kv_len = step[STEP_KV_LEN_GLOBAL];
-    const uint32_t chunk = (kv_len + n_splits - 1) / n_splits;
-    const uint32_t t_begin = min((uint32_t)split * chunk, kv_len);
-    const uint32_t t_end = min(t_begin + chunk, kv_len);
-    const uint32_t s_begin = t_begin / STAGE_TOK;
-    const uint32_t n_iter = t_begin < t_end ? (t_end + STAGE_TOK - 1) / STAGE_TOK - s_begin : 0;
+    const bool active = kvh < (int)n_kv;  // idle warps of the last CTA when n_kv * SUB is not a multiple of 4
+    const int g = lane >> 2, t4 = lane & 3;
+    const uint32_t rows = m_q * G;
 
     if (lane == 0) {
+        tma_prefetch_desc(&tm_kq);
+        tma_prefetch_desc(&tm_vq);
         for (int i = 0; i < NSTAGES; i++) mbar_init(&sm.full[warp][i], 1);
         mbar_fence_init();
     }
+    const uint32_t kv_len = __ldg(step + STEP_KV_LEN_GLOBAL);
+    const uint32_t chunk = (kv_len + n_splits - 1) / n_splits;
+    const uint32_t t_begin = min((uint32_t)split * chunk, kv_len);
+    const uint32_t t_end = min(t_begin + chunk, kv_len);
+    const uint32_t s_begin = t_begin / STAGE_TOK + sub;  // this warp's first stage; it then strides by SUB
+    const uint32_t n_stages = t_begin < t_end ? (t_end + STAGE_TOK - 1) / STAGE_TOK - t_begin / STAGE_TOK : 0;
+    const uint32_t n_iter = active && n_stages > (uint32_t)sub ? (n_stages - sub + SUB - 1) / SUB : 0;
     __syncwarp();
-    if (kvh >= (int)n_kv) return;  // a CTA of the last group when n_kv is not a multiple of 4
 
     // Physical page of the stage with index `stage` (tokens 16*stage ..), checked, never followed blindly.
     auto lookup = [&](uint32_t stage) -> uint32_t {
@@ -152,11 +160,11 @@ __global__ void __launch_bounds__(WPC * 32, MIN_CTAS)
         uint32_t pp = 0;
         if (lp < table_len) {
             pp = __ldg(page_table + lp);
-        } else if (lane == 0) {
+        } else {
             report_error(status, DEV_ERR_BOUNDS, 302, lp, table_len);
         }
         if (pp >= pool_pages) {
-            if (lane == 0) report_error(status, DEV_ERR_BOUNDS, 303, pp, pool_pages);
+            report_error(status, DEV_ERR_BOUNDS, 303, pp, pool_pages);
             pp = 0;
         }
         return pp;
@@ -164,7 +172,7 @@ __global__ void __launch_bounds__(WPC * 32, MIN_CTAS)
     // Lane 0 only: start the four TMA copies of iteration `it` into slot it % NSTAGES.
     auto issue = [&](uint32_t it, uint32_t pp) {
         const int st = it % NSTAGES;
-        const uint32_t tok0 = (s_begin + it) * STAGE_TOK;
+        const uint32_t tok0 = (s_begin + it * SUB) * STAGE_TOK;
         const int row = (int)(pp * page + tok0 % page);
         uint64_t* bar = &sm.full[warp][st];
         fence_proxy_async_smem();  // the slot's previous contents were read through the generic proxy
@@ -174,19 +182,21 @@ __global__ void __launch_bounds__(WPC * 32, MIN_CTAS)
         tma_load_3d(sm.vq[warp][st], &tm_vq, bar, 0, kvh, row);
         tma_load_2d(sm.vs[warp][st], &tm_vs, bar, (kvh >> 1) * 8, row);
     };
+    // Start the pipeline before anything else: lanes 0..NSTAGES-1 fetch the first page entries side
+    // by side (one memory latency, not NSTAGES), lane 0 issues; the Q loads below overlap the copies.
     {
         const uint32_t n_pre = min(n_iter, (uint32_t)NSTAGES);
+        uint32_t my_pp = 0;
+        if ((uint32_t)lane < n_pre) my_pp = lookup(s_begin + lane * SUB);
         for (uint32_t it = 0; it < n_pre; ++it) {
-            const uint32_t pp = lookup(s_begin + it);
+            const uint32_t pp = __shfl_sync(0xffffffffu, my_pp, it);
             if (lane == 0) issue(it, pp);
         }
     }
     // The page of the next stage to be issued is looked up one iteration early, so the load's
     // latency is covered by a tile of work.
-    uint32_t next_pp = n_iter > (uint32_t)NSTAGES ? lookup(s_begin + NSTAGES) : 0;
-
-    const int g = lane >> 2, t4 = lane & 3;
-    const uint32_t rows = m_q * G;
+    uint32_t next_pp = 0;
+    if (n_iter > (uint32_t)NSTAGES && lane == 0) next_pp = lookup(s_begin + NSTAGES * SUB);
 
     // MMA roles.  QK^T: A = K (16 tokens x 16 dims of chunk c), B = Q^T (16 dims x 8 query rows).
     //            PV  : A = V^T (16 dims of chunk c x 16 tokens), B = P'^T (16 tokens x 8 query rows).
@@ -198,7 +208,7 @@ __global__ void __launch_bounds__(WPC * 32, MIN_CTAS)
     uint32_t qb[8][2];
     float cinit[4][2];  // -1152 * (sum of q over block b) for query rows 2*t4 + e
     {
-        const bool q_live = (uint32_t)g < rows;
+        const bool q_live = active && (uint32_t)g < rows;
         const __half* qrow = q + ((size_t)(g / G) * n_q + kvh * G + g % G) * HD;
 #pragma unroll
         for (int b = 0; b < 4; b++) {
@@ -250,7 +260,7 @@ __global__ void __launch_bounds__(WPC * 32, MIN_CTAS)
     for (uint32_t it = 0; it < n_iter; ++it) {
         const int st = it % NSTAGES;
         mbar_wait(&sm.full[warp][st], (it / NSTAGES) & 1, status, 305, failed);
-        const int tok0 = (int)((s_begin + it) * STAGE_TOK);
+        const int tok0 = (int)((s_begin + it * SUB) * STAGE_TOK);
         const uint32_t kq_base = smem_u32(sm.kq[warp][st]), vq_base = smem_u32(sm.vq[warp][st]);
 
         // ---- S = K Q^T per 32-wide block, then the block scales: s[th][e] = score of token g + 8*th
@@ -354,28 +364,74 @@ __global__ void __launch_bounds__(WPC * 32, MIN_CTAS)
 
         // Refill this slot for iteration it + NSTAGES; every lane is done reading it.
         __syncwarp();
-        if (it + NSTAGES < n_iter) {
-            if (lane == 0) issue(it + NSTAGES, next_pp);
-            if (it + NSTAGES + 1 < n_iter) next_pp = lookup(s_begin + it + NSTAGES + 1);
+        if (lane == 0 && it + NSTAGES < n_iter) {
+            issue(it + NSTAGES, next_pp);
+            if (it + NSTAGES + 1 < n_iter) next_pp = lookup(s_begin + (it + NSTAGES + 1) * SUB);
         }
     }
 
-    // ---- this head's partial for the split, straight from registers ----------------------------------
+    // ---- remove the +1152 offsets, total the denominators --------------------------------------------
 #pragma unroll
-    for (int e = 0; e < 2; e++) {
-        const uint32_t r = 2 * t4 + e;  // query row = token index * G + head within the group
-        const float l_row = tok_sum(l_part[e]);
-        if (r < rows) {
-            float* dst = part + (((size_t)(r / G) * n_q + kvh * G + r % G) * n_splits + split) * (HD + 2);
+    for (int c = 0; c < 8; c++) {
 #pragma unroll
-            for (int c = 0; c < 8; c++) {
-                const float corr = OFFSET * osum[c >> 1][e];
-                // dims 16c + 2g and 16c + 2g + 1; rows are 520 bytes, so 8-byte aligned stores
-                *reinterpret_cast<float2*>(dst + 16 * c + 2 * g) = make_float2(o[c][e] - corr, o[c][2 + e] - corr);
+        for (int i = 0; i < 4; i++) o[c][i] -= OFFSET * osum[c >> 1][i];
+    }
+    float l_row[2] = {tok_sum(l_part[0]), tok_sum(l_part[1])};
+
+    // ---- merge the SUB sub-splits of a head in fixed order (sub 0 <- 1 <- 2 <- 3) ----------------------
+    // A warp's K ring is free by now (all its copies were consumed) and holds [8 rows][130] floats.
+    if (SUB > 1) {
+        float* mine = reinterpret_cast<float*>(sm.kq[warp][0]);
+        if (sub != 0) {
+#pragma unroll
+            for (int e = 0; e < 2; e++) {
+                float* dst = mine + (2 * t4 + e) * (HD + 2);
+#pragma unroll
+                for (int c = 0; c < 8; c++) *reinterpret_cast<float2*>(dst + 16 * c + 2 * g) = make_float2(o[c][e], o[c][2 + e]);
+                if (g == 0) {
+                    dst[HD] = m_run[e];
+                    dst[HD + 1] = l_row[e];
+                }
             }
-            if (g == 0) {
-                dst[HD] = m_run[e] == NEG_SENTINEL ? NEG_SENTINEL : m_run[e] * 0.6931471805599453f;  // back to natural log
-                dst[HD + 1] = l_row;
+        }
+        __syncthreads();
+        if (sub == 0) {
+#pragma unroll
+            for (int u = 1; u < SUB; u++) {
+                const float* other = reinterpret_cast<const float*>(sm.kq[warp + u][0]);
+#pragma unroll
+                for (int e = 0; e < 2; e++) {
+                    const float* src = other + (2 * t4 + e) * (HD + 2);
+                    const float mo = src[HD], lo = src[HD + 1];
+                    const float mn = fmaxf(m_run[e], mo);
+                    const float fa = ex2(m_run[e] - mn), fb = ex2(mo - mn);
+                    m_run[e] = mn;
+                    l_row[e] = l_row[e] * fa + lo * fb;
+#pragma unroll
+                    for (int c = 0; c < 8; c++) {
+                        const float2 v = *reinterpret_cast<const float2*>(src + 16 * c + 2 * g);
+                        o[c][e] = o[c][e] * fa + v.x * fb;
+                        o[c][2 + e] = o[c][2 + e] * fa + v.y * fb;
+                    }
+                }
+            }
+        }
+    }
+
+    // ---- the split's partial, straight from registers ------------------------------------------------
+    if (active && sub == 0) {
+#pragma unroll
+        for (int e = 0; e < 2; e++) {
+            const uint32_t r = 2 * t4 + e;  // query row = token index * G + head within the group
+            if (r < rows) {
+                float* dst = part + (((size_t)(r / G) * n_q + kvh * G + r % G) * n_splits + split) * (HD + 2);
+                // dims 16c + 2g and 16c + 2g + 1; rows are 520 bytes, so 8-byte aligned stores
+#pragma unroll
+                for (int c = 0; c < 8; c++) *reinterpret_cast<float2*>(dst + 16 * c + 2 * g) = make_float2(o[c][e], o[c][2 + e]);
+                if (g == 0) {
+                    dst[HD] = m_run[e] == NEG_SENTINEL ? NEG_SENTINEL : m_run[e] * 0.6931471805599453f;  // back to natural log
+                    dst[HD + 1] = l_row[e];
+                }
             }
         }
     }
@@ -405,7 +461,7 @@ int encode_pool_maps(const LaunchArgs& a, CUtensorMap (&tm)[4], const void* cons
     return 0;
 }
 
-template <int NSTAGES, int MIN_CTAS>
+template <int NSTAGES, int MIN_CTAS, int SUB>
 cudaError_t launch_decode_variant(cudaStream_t stream, int device, const CUtensorMap (&tm)[4], const __half* q,
                                   const uint32_t* page_table, uint32_t table_len, uint32_t page, uint32_t pool_pages, float* part,
                                   const uint32_t* step, uint32_t n_kv, uint32_t n_splits, float scale, uint32_t m_q, uint32_t* status)
@@ -414,37 +470,39 @@ cudaError_t launch_decode_variant(cudaStream_t stream, int device, const CUtenso
     const size_t smem = sizeof(Smem) + 1024;
     static bool attr_set[64] = {};
     if (device >= 0 && device < 64 && !attr_set[device]) {
-        cudaError_t e = cudaFuncSetAttribute(decode_paged_kernel<NSTAGES, MIN_CTAS>, cudaFuncAttributeMaxDynamicSharedMemorySize,
-                                             (int)smem);
+        cudaError_t e = cudaFuncSetAttribute(decode_paged_kernel<NSTAGES, MIN_CTAS, SUB>,
+                                             cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
         if (e != cudaSuccess) return e;
         attr_set[device] = true;
     }
-    decode_paged_kernel<NSTAGES, MIN_CTAS><<<dim3((n_kv + WPC - 1) / WPC, n_splits), WPC * 32, smem, stream>>>(
+    const uint32_t ctas_x = (n_kv * SUB + WPC - 1) / WPC;
+    decode_paged_kernel<NSTAGES, MIN_CTAS, SUB><<<dim3(ctas_x, n_splits), WPC * 32, smem, stream>>>(
         tm[0], tm[1], tm[2], tm[3], q, page_table, table_len, page, pool_pages, part, step, n_kv, n_splits, scale, m_q, status);
     return cudaGetLastError();
 }
 
-// Pipeline shape.  Default: 4 stages of 4.5 KB per warp = 72 KB per CTA, three CTAs (12 warps) per
-// SM at up to 168 registers.  SGB_DECODE_PIPELINE=3x4 selects three stages and four CTAs (16 warps)
-// per SM at 128 registers; it exists for tuning and changes no result bit.
-int pipeline_choice()
+// Shape of the launch.  Three 4.5 KB stages per warp = 54 KB per CTA and 128 registers per thread let
+// four CTAs = 16 warps live on an SM.  The number of sub-splits per (kv head, split) is the largest
+// of 4, 2, 1 for which all warps still fit on the GPU at once (one wave): extra waves cost more
+// than the parallelism buys.  SGB_DECODE_SUB=1|2|4 overrides the choice (tuning aid; results agree
+// within rounding, each choice is bit-reproducible).
+cudaError_t launch_decode(cudaStream_t stream, int device, int sm_count, const CUtensorMap (&tm)[4], const __half* q,
+                          const uint32_t* page_table, uint32_t table_len, uint32_t page, uint32_t pool_pages, float* part,
+                          const uint32_t* step, uint32_t n_kv, uint32_t n_splits, float scale, uint32_t m_q, uint32_t* status)
 {
-    static int choice = [] {
-        const char* e = getenv("SGB_DECODE_PIPELINE");
-        return (e && e[0] == '3') ? 1 : 0;
+    static const int forced = [] {
+        const char* e = getenv("SGB_DECODE_SUB");
+        return e ? atoi(e) : 0;
     }();
-    return choice;
-}
-
-cudaError_t launch_decode(cudaStream_t stream, int device, const CUtensorMap (&tm)[4], const __half* q, const uint32_t* page_table,
-                          uint32_t table_len, uint32_t page, uint32_t pool_pages, float* part, const uint32_t* step, uint32_t n_kv,
-                          uint32_t n_splits, float scale, uint32_t m_q, uint32_t* status)
-{
-    if (pipeline_choice())
-        return launch_decode_variant<3, 4>(stream, device, tm, q, page_table, table_len, page, pool_pages, part, step, n_kv, n_splits,
-                                           scale, m_q, status);
-    return launch_decode_variant<4, 3>(stream, device, tm, q, page_table, table_len, page, pool_pages, part, step, n_kv, n_splits,
-                                       scale, m_q, status);
+    const uint64_t slots = (uint64_t)(sm_count > 0 ? sm_count : 148) * 16;
+    const uint64_t tasks = (uint64_t)n_kv * n_splits;
+    int sub = tasks * 4 <= slots ? 4 : tasks * 2 <= slots ? 2 : 1;
+    if (forced == 1 || forced == 2 || forced == 4) sub = forced;
+#define SGB_DECODE_ARGS stream, device, tm, q, page_table, table_len, page, pool_pages, part, step, n_kv, n_splits, scale, m_q, status
+    if (sub == 4) return launch_decode_variant<3, 4, 4>(SGB_DECODE_ARGS);
+    if (sub == 2) return launch_decode_variant<3, 4, 2>(SGB_DECODE_ARGS);
+    return launch_decode_variant<3, 4, 1>(SGB_DECODE_ARGS);
+#undef SGB_DECODE_ARGS
 }
 
 }  // namespace
@@ -481,7 +539,7 @@ int launch_decode_paged_q8kv_d128(const LaunchArgs& a)
     const void* const quants[2] = {a.b[1].ptr, a.b[3].ptr};
     const void* const scales[2] = {a.b[2].ptr, a.b[4].ptr};
     if (int r = encode_pool_maps(a, tm, quants, scales, n_kv, pool_rows)) return r;
-    const cudaError_t e = launch_decode(a.stream, a.device, tm, (const __half*)a.b[0].ptr, (const uint32_t*)a.b[5].ptr,
+    const cudaError_t e = launch_decode(a.stream, a.device, a.sm_count, tm, (const __half*)a.b[0].ptr, (const uint32_t*)a.b[5].ptr,
                                         (uint32_t)(a.b[5].bytes / 4), p.page, (uint32_t)(pool_rows / p.page), (float*)a.b[6].ptr,
                                         (const uint32_t*)a.b[7].ptr, n_kv, p.n_splits, p.scale, m_q, a.status);
     ++*a.launches;
@@ -608,7 +666,9 @@ extern "C" int sgb_decode_paged_q8kv_d128_noalloc(int device, void* stream, cons
     if (int r = encode_pool_maps(a, tm, quants, scales, n_kv_heads, pool_rows)) return set_last_error(r, err);
     cudaStream_t s = (cudaStream_t)stream;
     noalloc_step_kernel<<<1, 1, 0, s>>>(kv_len);
-    e = launch_decode(s, device, tm, (const __half*)q, page_table, table_len, page, (uint32_t)(pool_rows / page), scratch, step,
+    int sm_count = 0;
+    cudaDeviceGetAttribute(&sm_count, cudaDevAttrMultiProcessorCount, device);
+    e = launch_decode(s, device, sm_count, tm, (const __half*)q, page_table, table_len, page, (uint32_t)(pool_rows / page), scratch, step,
                       n_kv_heads, n_splits, scale, m_q, status);
     if (e != cudaSuccess) return set_last_error(4, std::string("decode_noalloc: launch: ") + cudaGetErrorString(e));
     noalloc_reduce_kernel<<<m_q * n_kv_heads * G, HD, 0, s>>>(out, n_splits);

@@ -9,15 +9,16 @@
 //
 // One CTA = 64 query tokens x the 2 query heads of one kv head = 128 rows of S and O, so both
 // heads share every K/V tile (GQA grouping).  Per 64-key tile:
-//   TMA (128B swizzle, no multicast) -> smem K, V        thread 0
-//   S[128x64]  = Q K^T   tcgen05.mma kind::f16, D in TMEM  thread 0, 8 instructions (K = 16 each)
+//   TMA (128B swizzle, no multicast) -> smem K, V              loader warp
+//   S[128x64]  = Q K^T   tcgen05.mma kind::f16, D in TMEM      MMA warp, 8 instructions (K = 16 each)
 //   row softmax in registers: thread r owns TMEM lane r (tcgen05.ld 32x32b), base-2 exponent,
 //       running max raised only when it grows by > 2^8; masked tiles only at the band edges,
-//       tiles wholly outside [qpos+1-window, qpos] are never visited
+//       tiles wholly outside [qpos+1-window, qpos] are never visited           4 softmax warps
 //   P -> smem as f16 in the K-major swizzled layout, fence.proxy.async
 //   O[128x128] += P V    tcgen05.mma, V as the MN-major B operand straight from its [key][dim] tile
-// Two CTAs fit per SM (112 KB smem, 256 TMEM columns each), so one CTA's softmax overlaps the
-// other's MMAs.  Every mbarrier wait is bounded; TMEM is always freed.
+// S is double-buffered in TMEM and the three roles talk through mbarriers only, so Q K^T of the
+// next tile and P V of the previous one run while the softmax warps work.  Two CTAs fit per SM
+// (112 KB smem, 256 TMEM columns each).  Every mbarrier wait is bounded; TMEM is always freed.
 #include "sgb_common.cuh"
 #include "sgb_kernels.h"
 
@@ -33,17 +34,19 @@ constexpr int G = 2;
 constexpr int BLOCK_TOK = 64;   // query tokens per CTA
 constexpr int BLOCK_M = 128;    // rows = tokens x G
 constexpr int BLOCK_N = 64;     // keys per tile
-constexpr int FLASH_THREADS = 128;
+constexpr int SOFTMAX_THREADS = 128;
+constexpr int MMA_WARP = 4, LOAD_WARP = 5;
+constexpr int FLASH_THREADS = 192;
 constexpr int KV_STAGES = 2;
 constexpr uint32_t HALF_TILE = 64 * 128;           // one [64 rows][128 B] box
 constexpr uint32_t Q_BYTES = 2 * 2 * HALF_TILE;    // 2 dim-halves x 128 rows
 constexpr uint32_t KV_TILE_BYTES = 2 * HALF_TILE;  // 2 dim-halves x 64 keys
 constexpr uint32_t TMEM_COLS = 256;
-constexpr uint32_t TMEM_S = 0;    // S: 64 f32 columns
-constexpr uint32_t TMEM_O = 64;   // O: 128 f32 columns
+constexpr uint32_t TMEM_S = 0;     // S: two buffers of 64 f32 columns
+constexpr uint32_t TMEM_O = 128;   // O: 128 f32 columns
 constexpr float RESCALE_T = 8.0f;
 
-// 112 KB of tiles + 64 B of barriers.  Two CTAs must fit in the SM's 228 KB next to the 1 KB the
+// 112 KB of tiles + 128 B of barriers.  Two CTAs must fit in the SM's 228 KB next to the 1 KB the
 // system reserves per CTA, so the struct is NOT padded to its 1024-byte tile alignment: the dynamic
 // shared-memory base is declared 1024-aligned instead (and checked at run time).
 struct FlashSmem {
@@ -51,15 +54,17 @@ struct FlashSmem {
     uint8_t k[KV_STAGES][2][HALF_TILE];      // [stage][dim half][64 keys x 128 B]
     uint8_t v[KV_STAGES][2][HALF_TILE];
     uint8_t p[2 * HALF_TILE];                // [128 rows x 128 B] = 64 f16 keys per row
-    uint64_t full_k[KV_STAGES];
+    uint64_t full_k[KV_STAGES];              // TMA -> MMA warp
     uint64_t full_v[KV_STAGES];
+    uint64_t s_ready[2];                     // MMA commit: S[b] holds Q K^T of a tile
+    uint64_t s_free[2];                      // 128 softmax threads: S[b] has been read
     uint64_t q_bar;
-    uint64_t s_bar;
-    uint64_t pv_bar;
+    uint64_t p_ready;                        // 128 softmax threads: P is in shared memory
+    uint64_t pv_done;                        // MMA commit: O += P V of a tile has completed
     uint32_t tmem_base;
-    uint32_t pad;
+    uint32_t pad[9];
 };
-static_assert(sizeof(FlashSmem) == 7 * 2 * HALF_TILE + 64, "tiles + barriers, no padding");
+static_assert(sizeof(FlashSmem) == 7 * 2 * HALF_TILE + 128, "tiles + barriers, no padding");
 static_assert(2 * (sizeof(FlashSmem) + 1024) <= 228 * 1024, "two CTAs per SM");
 
 struct FlashParams {
@@ -81,6 +86,11 @@ struct Tile {
     int64_t lo, hi; // positions of this source that are real: [lo, hi]
 };
 
+// Roles: warps 0-3 = softmax (thread r owns row r of S and O), warp 4 = MMA issue (one thread),
+// warp 5 = TMA loads (one thread).  Per tile j the tensor pipe runs, in order, ... PV(j-1) QK(j+1)
+// PV(j) QK(j+2) ...: S is double-buffered in TMEM, so QK(j+1) and PV(j-1) execute while the softmax
+// warps work on tile j, and the softmax is the only thing on the critical path of a CTA; the second
+// CTA on the SM fills the tensor pipe's remaining gaps.
 template <bool TWO_SRC>
 __global__ void __launch_bounds__(FLASH_THREADS, 2) flash_prefill_kernel(const __grid_constant__ CUtensorMap tm_q,
                                                                          const __grid_constant__ CUtensorMap tm_k0,
@@ -107,6 +117,7 @@ __global__ void __launch_bounds__(FLASH_THREADS, 2) flash_prefill_kernel(const _
     // ---- which key tiles this CTA visits -------------------------------------------------------------
     const int64_t first_qpos = q0 + m0, last_qpos = q0 + m0 + tok_in_tile - 1;
     const int64_t band_lo = (prm.window != 0 && first_qpos + 1 > (int64_t)prm.window) ? first_qpos + 1 - prm.window : 0;
+    const int64_t last_lo = (prm.window != 0 && last_qpos + 1 > (int64_t)prm.window) ? last_qpos + 1 - prm.window : 0;
     int n_hist, n_tiles;
     int64_t hist_pos0 = 0, chunk_c0 = 0;
     if (TWO_SRC) {
@@ -146,14 +157,13 @@ __global__ void __launch_bounds__(FLASH_THREADS, 2) flash_prefill_kernel(const _
         for (int i = 0; i < KV_STAGES; i++) {
             mbar_init(&sm.full_k[i], 1);
             mbar_init(&sm.full_v[i], 1);
+            mbar_init(&sm.s_ready[i], 1);
+            mbar_init(&sm.s_free[i], SOFTMAX_THREADS);
         }
         mbar_init(&sm.q_bar, 1);
-        mbar_init(&sm.s_bar, 1);
-        mbar_init(&sm.pv_bar, 1);
+        mbar_init(&sm.p_ready, SOFTMAX_THREADS);
+        mbar_init(&sm.pv_done, 1);
         mbar_fence_init();
-        tma_prefetch_desc(&tm_q);
-        tma_prefetch_desc(&tm_k0);
-        tma_prefetch_desc(&tm_v0);
     }
     if (warp == 0) {
         tmem_alloc(&sm.tmem_base, TMEM_COLS);
@@ -163,174 +173,186 @@ __global__ void __launch_bounds__(FLASH_THREADS, 2) flash_prefill_kernel(const _
     __syncthreads();
     tc_fence_after_sync();
     const uint32_t tmem = sm.tmem_base;
-
-    auto load_k = [&](int it) {
-        const Tile t = tile_at(it);
-        const int st = it % KV_STAGES;
-        const CUtensorMap* mk = (TWO_SRC && t.src) ? &tm_k1 : &tm_k0;
-        mbar_arrive_expect_tx(&sm.full_k[st], KV_TILE_BYTES);
-        tma_load_3d(sm.k[st][0], mk, &sm.full_k[st], 0, kvh, t.row0);
-        tma_load_3d(sm.k[st][1], mk, &sm.full_k[st], 64, kvh, t.row0);
-    };
-    auto load_v = [&](int it) {
-        const Tile t = tile_at(it);
-        const int st = it % KV_STAGES;
-        const CUtensorMap* mv = (TWO_SRC && t.src) ? &tm_v1 : &tm_v0;
-        mbar_arrive_expect_tx(&sm.full_v[st], KV_TILE_BYTES);
-        tma_load_3d(sm.v[st][0], mv, &sm.full_v[st], 0, kvh, t.row0);
-        tma_load_3d(sm.v[st][1], mv, &sm.full_v[st], 64, kvh, t.row0);
-    };
-    constexpr uint32_t IDESC_QK = umma_idesc_f16(BLOCK_M, BLOCK_N, 0, 0);
-    constexpr uint32_t IDESC_PV = umma_idesc_f16(BLOCK_M, HD, 0, 1);
     bool failed = false;
-    // S = Q K^T for tile `it` (8 MMAs of K = 16), issued by thread 0 once K(it) has landed.
-    auto issue_qk = [&](int it) {
-        const int st = it % KV_STAGES;
-        mbar_wait(&sm.full_k[st], (it / KV_STAGES) & 1, prm.status, 402, failed);
-        tc_fence_after_sync();
-#pragma unroll
-        for (int h = 0; h < 2; h++) {
-#pragma unroll
-            for (int j = 0; j < 4; j++) {
-                const uint64_t da = umma_desc_sw128(smem_u32(sm.q[h]) + j * 32, 16, 1024);
-                const uint64_t db = umma_desc_sw128(smem_u32(sm.k[st][h]) + j * 32, 16, 1024);
-                umma_f16_ss(tmem + TMEM_S, da, db, IDESC_QK, (h | j) ? 1u : 0u);
+
+    if (warp == LOAD_WARP) {
+        // ======================= TMA loads =======================
+        if ((tid & 31) == 0) {
+            tma_prefetch_desc(&tm_q);
+            tma_prefetch_desc(&tm_k0);
+            tma_prefetch_desc(&tm_v0);
+            auto load_k = [&](int it) {
+                const Tile t = tile_at(it);
+                const int st = it % KV_STAGES;
+                const CUtensorMap* mk = (TWO_SRC && t.src) ? &tm_k1 : &tm_k0;
+                mbar_arrive_expect_tx(&sm.full_k[st], KV_TILE_BYTES);
+                tma_load_3d(sm.k[st][0], mk, &sm.full_k[st], 0, kvh, t.row0);
+                tma_load_3d(sm.k[st][1], mk, &sm.full_k[st], 64, kvh, t.row0);
+            };
+            auto load_v = [&](int it) {
+                const Tile t = tile_at(it);
+                const int st = it % KV_STAGES;
+                const CUtensorMap* mv = (TWO_SRC && t.src) ? &tm_v1 : &tm_v0;
+                mbar_arrive_expect_tx(&sm.full_v[st], KV_TILE_BYTES);
+                tma_load_3d(sm.v[st][0], mv, &sm.full_v[st], 0, kvh, t.row0);
+                tma_load_3d(sm.v[st][1], mv, &sm.full_v[st], 64, kvh, t.row0);
+            };
+            mbar_arrive_expect_tx(&sm.q_bar, Q_BYTES);
+            tma_load_3d(sm.q[0], &tm_q, &sm.q_bar, 0, kvh * G, (int)m0);
+            tma_load_3d(sm.q[1], &tm_q, &sm.q_bar, 64, kvh * G, (int)m0);
+            load_k(0);
+            if (n_tiles > 1) load_k(1);
+            load_v(0);
+            if (n_tiles > 1) load_v(1);
+            for (int j = 0; j + 2 < n_tiles; ++j) {
+                const int b = j % KV_STAGES;
+                // K stage b is free once QK(j) has completed, V stage b once PV(j) has.
+                mbar_wait(&sm.s_ready[b], (j / 2) & 1, prm.status, 411, failed);
+                load_k(j + 2);
+                mbar_wait(&sm.pv_done, j & 1, prm.status, 412, failed);
+                load_v(j + 2);
             }
         }
-    };
-
-    // The tensor pipe runs in order, so one commit after "PV(it), QK(it+1)" tells the CTA three
-    // things at once when s_bar flips: S(it+1) is ready, P and V(it) have been consumed, O is stable.
-    if (tid == 0) {
-        mbar_arrive_expect_tx(&sm.q_bar, Q_BYTES);
-        tma_load_3d(sm.q[0], &tm_q, &sm.q_bar, 0, kvh * G, (int)m0);
-        tma_load_3d(sm.q[1], &tm_q, &sm.q_bar, 64, kvh * G, (int)m0);
-        load_k(0);
-        load_v(0);
-        if (n_tiles > 1) load_k(1);
-        mbar_wait(&sm.q_bar, 0, prm.status, 401, failed);
-        issue_qk(0);
-        umma_commit(&sm.s_bar);
-    }
-
-    // Row r of the tile <-> TMEM lane r <-> thread r: token m0 + r/2, query head kvh*2 + r%2.
-    const int r = tid;
-    const uint32_t tok = m0 + (uint32_t)(r >> 1);
-    const int64_t qpos = q0 + tok;
-    const int64_t row_lo = (prm.window != 0 && qpos + 1 > (int64_t)prm.window) ? qpos + 1 - prm.window : 0;
-    const float scale2 = prm.scale * 1.4426950408889634f;
-    const uint32_t lane_addr = tmem + ((uint32_t)(warp * 32) << 16);
-
-    float m_run = NEG_SENTINEL, l_run = 0.0f;
-
-    for (int it = 0; it < n_tiles; ++it) {
-        const int st = it % KV_STAGES;
-        const Tile t = tile_at(it);
-
-        mbar_wait(&sm.s_bar, it & 1, prm.status, 403, failed);
-        tc_fence_after_sync();
-        if (tid == 0) {
-            // S(it) ready => QK(it) and PV(it-1) are done: K stage it%2 and V stage (it+1)%2 are free.
-            if (it + 1 < n_tiles) load_v(it + 1);
-            if (it + 2 < n_tiles) load_k(it + 2);
-        }
-
-        // ---- softmax on this thread's row -----------------------------------------------------------
-        uint32_t sv[64];
-        {
-            uint32_t a[32], b[32];
-            tmem_ld_32x32b_x32(lane_addr + TMEM_S, a);
-            tmem_ld_32x32b_x32(lane_addr + TMEM_S + 32, b);
-            tc_wait_ld();
+    } else if (warp == MMA_WARP) {
+        // ======================= MMA issue =======================
+        if ((tid & 31) == 0) {
+            constexpr uint32_t IDESC_QK = umma_idesc_f16(BLOCK_M, BLOCK_N, 0, 0);
+            constexpr uint32_t IDESC_PV = umma_idesc_f16(BLOCK_M, HD, 0, 1);
+            // S[j % 2] = Q K(j)^T: 8 MMAs of K = 16, once K(j) has landed.
+            auto issue_qk = [&](int j) {
+                const int b = j % KV_STAGES;
+                mbar_wait(&sm.full_k[b], (j / KV_STAGES) & 1, prm.status, 402, failed);
+                tc_fence_after_sync();
 #pragma unroll
-            for (int j = 0; j < 32; j++) {
-                sv[j] = a[j];
-                sv[32 + j] = b[j];
+                for (int h = 0; h < 2; h++) {
+#pragma unroll
+                    for (int kk = 0; kk < 4; kk++) {
+                        const uint64_t da = umma_desc_sw128(smem_u32(sm.q[h]) + kk * 32, 16, 1024);
+                        const uint64_t db = umma_desc_sw128(smem_u32(sm.k[b][h]) + kk * 32, 16, 1024);
+                        umma_f16_ss(tmem + TMEM_S + b * BLOCK_N, da, db, IDESC_QK, (h | kk) ? 1u : 0u);
+                    }
+                }
+                umma_commit(&sm.s_ready[b]);
+            };
+            mbar_wait(&sm.q_bar, 0, prm.status, 401, failed);
+            issue_qk(0);
+            if (n_tiles > 1) issue_qk(1);
+            for (int j = 0; j < n_tiles; ++j) {
+                const int b = j % KV_STAGES;
+                mbar_wait(&sm.p_ready, j & 1, prm.status, 403, failed);
+                mbar_wait(&sm.full_v[b], (j / KV_STAGES) & 1, prm.status, 405, failed);
+                tc_fence_after_sync();
+#pragma unroll
+                for (int kk = 0; kk < 4; kk++) {
+                    const uint64_t da = umma_desc_sw128(smem_u32(sm.p) + kk * 32, 16, 1024);
+                    const uint64_t db = umma_desc_sw128(smem_u32(sm.v[b][0]) + kk * 2048, HALF_TILE, 1024);
+                    umma_f16_ss(tmem + TMEM_O, da, db, IDESC_PV, (j | kk) ? 1u : 0u);
+                }
+                umma_commit(&sm.pv_done);
+                if (j + 2 < n_tiles) {
+                    // S[b] was read by the softmax warps before they produced P(j).
+                    mbar_wait(&sm.s_free[b], (j / 2) & 1, prm.status, 406, failed);
+                    issue_qk(j + 2);
+                }
             }
         }
-        // A tile needs per-element masks only where it crosses a band edge or a source boundary.
-        const bool tile_masked = t.pos0 + BLOCK_N - 1 > first_qpos || t.pos0 < (prm.window ? (last_qpos + 1 > (int64_t)prm.window ? last_qpos + 1 - prm.window : 0) : 0) ||
-                                 t.pos0 < t.lo || t.pos0 + BLOCK_N - 1 > t.hi;
-        float s2[64];
-        float mx = -INFINITY;
-        if (tile_masked) {
-            const int64_t hi = min(qpos, t.hi), lo = max(row_lo, t.lo);
-#pragma unroll
-            for (int j = 0; j < 64; j++) {
-                const int64_t pos = t.pos0 + j;
-                s2[j] = (pos >= lo && pos <= hi) ? __uint_as_float(sv[j]) * scale2 : -INFINITY;
-                mx = fmaxf(mx, s2[j]);
-            }
-        } else {
-#pragma unroll
-            for (int j = 0; j < 64; j++) {
-                s2[j] = __uint_as_float(sv[j]) * scale2;
-                mx = fmaxf(mx, s2[j]);
-            }
-        }
-        const bool grow = mx > m_run + RESCALE_T;
-        float corr = 1.0f;
-        if (grow) {
-            corr = ex2(m_run - mx);
-            m_run = mx;
-            l_run *= corr;
-        }
-        uint32_t pk[32];
-        float lsum = 0.0f;
-#pragma unroll
-        for (int j = 0; j < 32; j++) {
-            const float p0 = ex2(s2[2 * j] - m_run), p1 = ex2(s2[2 * j + 1] - m_run);
-            lsum += p0 + p1;
-            pk[j] = pack_half2(p0, p1);
-        }
-        l_run += lsum;
-        // P row r, 16-byte chunk c (keys 8c..8c+7) sits at chunk c ^ (r & 7) of its 128-byte row.
-        {
-            uint8_t* prow = sm.p + r * 128;
-#pragma unroll
-            for (int c = 0; c < 8; c++)
-                *reinterpret_cast<uint4*>(prow + ((c ^ (r & 7)) << 4)) = make_uint4(pk[4 * c], pk[4 * c + 1], pk[4 * c + 2], pk[4 * c + 3]);
-        }
-        // ---- rescale O where a row's max moved (O is only defined after the first PV) --------------
-        if (it > 0 && __any_sync(0xffffffffu, grow)) {
-#pragma unroll
-            for (int c = 0; c < 4; c++) {
-                uint32_t o[32];
-                tmem_ld_32x32b_x32(lane_addr + TMEM_O + 32 * c, o);
+    } else {
+        // ======================= softmax: row r of the tile <-> TMEM lane r <-> thread r =======================
+        // token m0 + r/2, query head kvh*2 + r%2
+        const int r = tid;
+        const uint32_t tok = m0 + (uint32_t)(r >> 1);
+        const int64_t qpos = q0 + tok;
+        const int64_t row_lo = (prm.window != 0 && qpos + 1 > (int64_t)prm.window) ? qpos + 1 - prm.window : 0;
+        const float scale2 = prm.scale * 1.4426950408889634f;  // > 0 (checked on the host)
+        const uint32_t lane_addr = tmem + ((uint32_t)(warp * 32) << 16);
+        float m_run = NEG_SENTINEL, l_run = 0.0f;
+
+        for (int it = 0; it < n_tiles; ++it) {
+            const int b = it % 2;
+            const Tile t = tile_at(it);
+            mbar_wait(&sm.s_ready[b], (it / 2) & 1, prm.status, 404, failed);
+            tc_fence_after_sync();
+            float v[64];
+            {
+                uint32_t a0[32], a1[32];
+                tmem_ld_32x32b_x32(lane_addr + TMEM_S + b * BLOCK_N, a0);
+                tmem_ld_32x32b_x32(lane_addr + TMEM_S + b * BLOCK_N + 32, a1);
                 tc_wait_ld();
 #pragma unroll
-                for (int j = 0; j < 32; j++) o[j] = __float_as_uint(__uint_as_float(o[j]) * corr);
-                tmem_st_32x32b_x32(lane_addr + TMEM_O + 32 * c, o);
+                for (int j = 0; j < 32; j++) {
+                    v[j] = __uint_as_float(a0[j]);
+                    v[32 + j] = __uint_as_float(a1[j]);
+                }
             }
-            tc_wait_st();
-        }
-        fence_proxy_async_smem();
-        tc_fence_before_sync();
-        __syncthreads();
+            tc_fence_before_sync();
+            mbar_arrive(&sm.s_free[b]);
 
-        if (tid == 0) {
-            mbar_wait(&sm.full_v[st], (it / KV_STAGES) & 1, prm.status, 405, failed);
-            tc_fence_after_sync();
+            // A tile needs per-element masks only where it crosses a band edge or a source boundary.
+            const bool tile_masked = t.pos0 + BLOCK_N - 1 > first_qpos || t.pos0 < last_lo || t.pos0 < t.lo || t.pos0 + BLOCK_N - 1 > t.hi;
+            if (tile_masked) {
+                const int64_t hi = min(qpos, t.hi), lo = max(row_lo, t.lo);
 #pragma unroll
-            for (int j = 0; j < 4; j++) {
-                const uint64_t da = umma_desc_sw128(smem_u32(sm.p) + j * 32, 16, 1024);
-                const uint64_t db = umma_desc_sw128(smem_u32(sm.v[st][0]) + j * 2048, HALF_TILE, 1024);
-                umma_f16_ss(tmem + TMEM_O, da, db, IDESC_PV, (it | j) ? 1u : 0u);
+                for (int j = 0; j < 64; j++) {
+                    const int64_t pos = t.pos0 + j;
+                    if (pos < lo || pos > hi) v[j] = -INFINITY;
+                }
             }
-            if (it + 1 < n_tiles) {
-                issue_qk(it + 1);
-                umma_commit(&sm.s_bar);
-            } else {
-                umma_commit(&sm.pv_bar);
+            // row max of the raw scores on four independent chains; scale2 > 0 commutes with max
+            float mx4[4] = {v[0], v[1], v[2], v[3]};
+#pragma unroll
+            for (int j = 4; j < 64; j++) mx4[j & 3] = fmaxf(mx4[j & 3], v[j]);
+            const float mx = fmaxf(fmaxf(mx4[0], mx4[1]), fmaxf(mx4[2], mx4[3])) * scale2;
+            const bool grow = mx > m_run + RESCALE_T;
+            float corr = 1.0f;
+            if (grow) {
+                corr = ex2(m_run - mx);
+                m_run = mx;
+                l_run *= corr;
             }
-        }
-    }
-    mbar_wait(&sm.pv_bar, 0, prm.status, 404, failed);
-    tc_fence_after_sync();
+            const float neg_m = -m_run;
+            uint32_t pk[32];
+            float ls4[4] = {0.0f, 0.0f, 0.0f, 0.0f};
+#pragma unroll
+            for (int j = 0; j < 32; j++) {
+                const float p0 = ex2(fmaf(v[2 * j], scale2, neg_m)), p1 = ex2(fmaf(v[2 * j + 1], scale2, neg_m));
+                ls4[j & 3] += p0 + p1;  // l in f32 from the unrounded p (attn_prefill_global_flash_sp.wgsl:147-156)
+                pk[j] = pack_half2(p0, p1);
+            }
+            l_run += (ls4[0] + ls4[1]) + (ls4[2] + ls4[3]);
 
-    // ---- epilogue: out = O / l.  The TMEM loads are warp-wide, so every thread takes part and only
-    // the stores are predicated (rows past the end of the chunk are not written). -------------------------
-    {
+            // P's buffer and O are only touched once PV of the previous tile has completed.
+            if (it > 0) {
+                mbar_wait(&sm.pv_done, (it - 1) & 1, prm.status, 407, failed);
+                tc_fence_after_sync();
+                if (__any_sync(0xffffffffu, grow)) {  // rescale O where a row's max moved
+#pragma unroll
+                    for (int c = 0; c < 4; c++) {
+                        uint32_t o[32];
+                        tmem_ld_32x32b_x32(lane_addr + TMEM_O + 32 * c, o);
+                        tc_wait_ld();
+#pragma unroll
+                        for (int j = 0; j < 32; j++) o[j] = __float_as_uint(__uint_as_float(o[j]) * corr);
+                        tmem_st_32x32b_x32(lane_addr + TMEM_O + 32 * c, o);
+                    }
+                    tc_wait_st();
+                }
+            }
+            // P row r, 16-byte chunk c (keys 8c..8c+7) sits at chunk c ^ (r & 7) of its 128-byte row.
+            {
+                uint8_t* prow = sm.p + r * 128;
+#pragma unroll
+                for (int c = 0; c < 8; c++)
+                    *reinterpret_cast<uint4*>(prow + ((c ^ (r & 7)) << 4)) = make_uint4(pk[4 * c], pk[4 * c + 1], pk[4 * c + 2], pk[4 * c + 3]);
+            }
+            fence_proxy_async_smem();
+            tc_fence_before_sync();
+            mbar_arrive(&sm.p_ready);
+        }
+        mbar_wait(&sm.pv_done, (n_tiles - 1) & 1, prm.status, 408, failed);
+        tc_fence_after_sync();
+
+        // ---- epilogue: out = O / l.  The TMEM loads are warp-wide, so every thread takes part and only
+        // the stores are predicated (rows past the end of the chunk are not written). ---------------------
         const bool live = (uint32_t)(r >> 1) < tok_in_tile;
         const float inv_l = 1.0f / l_run;
         float* orow = prm.out + ((size_t)(live ? tok : m0) * (prm.n_kv * G) + kvh * G + (r & 1)) * HD;
@@ -380,6 +402,7 @@ int run_flash(const LaunchArgs& a, const BufView& q, const BufView& k0, const Bu
               uint32_t ring)
 {
     if (n_kv == 0 || m_tokens == 0) return fail_validation(a, "flash prefill: groups must be [kv heads, query tokens]");
+    if (!(scale > 0.0f)) return fail_validation(a, "flash prefill: the softmax scale must be positive");
     const size_t n_q = (size_t)n_kv * G;
     if (q.bytes < (size_t)m_tokens * n_q * HD * 2) return fail_validation(a, "flash prefill: q buffer too small");
     if (out.bytes < (size_t)m_tokens * n_q * HD * 4) return fail_validation(a, "flash prefill: out buffer too small");
