@@ -170,21 +170,35 @@ def fisher_yates(seed, n):
     return np.random.default_rng(seed).permutation(n).astype(np.uint32)
 
 
-def timed(dev, fn, steps, warmup, dist=None, stamps_per_step=1):
+def timed(dev, fn, steps, warmup, dist=None, stamps_per_step=1, graph=False):
     """W untimed steps, then K steps bracketed by barrier + synchronize; returns (max-over-ranks
-    seconds for the K steps, per-step stamp deltas in ns as array [K, stamps_per_step])."""
+    seconds for the K steps, per-step stamp deltas in ns as array [K, stamps_per_step]).
+    graph=True records the K steps once and replays them as one CUDA graph, the way the reference
+    drives its decode step (record_graph / submit_blocking): steps of a few tens of microseconds
+    are otherwise bounded by the host's dispatch rate, not by the GPU."""
     torch = dev.torch
     for _ in range(warmup):
         fn(None, 0)
     dev.ctx.sync()
     timer = dev.ctx.new_timer(steps * stamps_per_step + 1)
+    g = None
+    if graph:
+        def record(_ctx):
+            for i in range(steps):
+                fn(timer, i * stamps_per_step)
+            timer.stamp(steps * stamps_per_step)
+        g = dev.ctx.record_graph(record)
+        dev.ctx.submit_blocking(g)  # one untimed replay
     if dist is not None:
         dist.barrier()
     torch.cuda.synchronize()
     before = dev.ctx.launch_count
-    for i in range(steps):
-        fn(timer, i * stamps_per_step)
-    timer.stamp(steps * stamps_per_step)
+    if g is not None:
+        dev.ctx.submit(g)
+    else:
+        for i in range(steps):
+            fn(timer, i * stamps_per_step)
+        timer.stamp(steps * stamps_per_step)
     dev.ctx.sync()
     torch.cuda.synchronize()
     launches = dev.ctx.launch_count - before
@@ -312,7 +326,7 @@ def run_decode(dev, rank, world, steps, warmup, dist, ctx_len, m_q, n_splits, se
                 dist.all_gather_into_tensor(gathered, mine)
             dev.ctx.dispatch(comb, dev.bind(b_gath, b_out), world, [rows, 1, 1])
 
-    total_s, deltas, launches = timed(dev, step, steps, warmup, dist, stamps_per_step=2)
+    total_s, deltas, launches = timed(dev, step, steps, warmup, dist, stamps_per_step=2, graph=(world == 1))
     kv_bytes = ctx_len * KV * (D + 8) * 2  # quants + scales, K and V
     algo = kv_bytes + m_q * H * D * 2 + m_q * H * D * 4 + (ctx_len // PAGE) * 4
     kern_us = float(np.median(deltas[:, 0])) * 1e-3

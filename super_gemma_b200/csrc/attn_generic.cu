@@ -229,35 +229,77 @@ __global__ void __launch_bounds__(GEN_THREADS) decode_generic_kernel(const __hal
     }
 }
 
-// Split-K combine, ascending split order (attn_reduce.wgsl:29-56).  Grid = rows.
+// Split-K combine (attn_reduce.wgsl:29-56).  Grid = rows, 128 threads.  The reference walks the
+// splits in ascending order rescaling as it goes; that chain of dependent loads costs a DRAM
+// latency per split, so here the same sum is formed in two steps with no dependence between
+// loads: M = max_s m_s, then acc = sum_s exp(m_s - M) * acc_s and l = sum_s exp(m_s - M) * l_s,
+// both summed in ascending split order (fixed order => bit-identical reruns).
 // OUT_MODE 0: f16(acc/l) (the reference), 1: f32 acc/l, 2: merged (acc, m, l) as f32[HD+2].
 // split_major = 0: part[(row*n + s)*(HD+2)]; 1: part[(s*rows + row)*(HD+2)] (per-rank blocks).
+constexpr int REDUCE_MAX_SPLITS = 1024;
+
 template <int HD, int OUT_MODE>
 __global__ void __launch_bounds__(128) reduce_kernel(const float* __restrict__ part, void* __restrict__ out, uint32_t n_splits,
                                                     int split_major)
 {
     constexpr int DPT = HD / 128;
+    __shared__ float w_s[REDUCE_MAX_SPLITS];
+    __shared__ float wl_s[REDUCE_MAX_SPLITS];
+    __shared__ float red[4];
     const size_t row = blockIdx.x, rows = gridDim.x;
-    const int d0 = threadIdx.x * DPT;
-    float m = NEG_SENTINEL, l = 0.0f, acc[DPT];
+    const int t = threadIdx.x;
+    const size_t s_stride = split_major ? rows * (HD + 2) : (size_t)(HD + 2);
+    const float* base = part + (split_major ? row : row * n_splits) * (HD + 2);
+
+    float mx = NEG_SENTINEL;
+    for (uint32_t s = t; s < n_splits; s += 128) {
+        const float ms = base[s * s_stride + HD];
+        w_s[s] = ms;
+        wl_s[s] = base[s * s_stride + HD + 1];
+        mx = fmaxf(mx, ms);
+    }
+#pragma unroll
+    for (int o = 16; o > 0; o >>= 1) mx = fmaxf(mx, __shfl_xor_sync(0xffffffffu, mx, o));
+    if ((t & 31) == 0) red[t >> 5] = mx;
+    __syncthreads();
+    const float m_all = fmaxf(fmaxf(red[0], red[1]), fmaxf(red[2], red[3]));
+    for (uint32_t s = t; s < n_splits; s += 128) {
+        const float w = __expf(w_s[s] - m_all);  // empty split: exp(-3e38 - m) = 0
+        w_s[s] = w;
+        wl_s[s] *= w;
+    }
+    __syncthreads();
+
+    float acc[DPT], l = 0.0f;
 #pragma unroll
     for (int d = 0; d < DPT; d++) acc[d] = 0.0f;
-    for (uint32_t s = 0; s < n_splits; s++) {
-        const float* p = part + (split_major ? ((size_t)s * rows + row) : (row * n_splits + s)) * (HD + 2);
-        const float ms = p[HD], ls = p[HD + 1];
-        const float m_new = fmaxf(m, ms);
-        const float ca = __expf(m - m_new), cb = __expf(ms - m_new);
+    uint32_t s = 0;
+    for (; s + 8 <= n_splits; s += 8) {
+        float v[8][DPT];
 #pragma unroll
-        for (int d = 0; d < DPT; d++) acc[d] = acc[d] * ca + p[d0 + d] * cb;
-        l = l * ca + ls * cb;
-        m = m_new;
+        for (int u = 0; u < 8; u++) {
+#pragma unroll
+            for (int d = 0; d < DPT; d++) v[u][d] = base[(s + u) * s_stride + t + 128 * d];
+        }
+#pragma unroll
+        for (int u = 0; u < 8; u++) {
+#pragma unroll
+            for (int d = 0; d < DPT; d++) acc[d] = fmaf(w_s[s + u], v[u][d], acc[d]);
+            l += wl_s[s + u];
+        }
     }
+    for (; s < n_splits; s++) {
+#pragma unroll
+        for (int d = 0; d < DPT; d++) acc[d] = fmaf(w_s[s], base[s * s_stride + t + 128 * d], acc[d]);
+        l += wl_s[s];
+    }
+
     if constexpr (OUT_MODE == 2) {
         float* o = reinterpret_cast<float*>(out) + row * (HD + 2);
 #pragma unroll
-        for (int d = 0; d < DPT; d++) o[d0 + d] = acc[d];
-        if (threadIdx.x == 0) {
-            o[HD] = m;
+        for (int d = 0; d < DPT; d++) o[t + 128 * d] = acc[d];
+        if (t == 0) {
+            o[HD] = m_all;
             o[HD + 1] = l;
         }
     } else {
@@ -265,9 +307,9 @@ __global__ void __launch_bounds__(128) reduce_kernel(const float* __restrict__ p
         for (int d = 0; d < DPT; d++) {
             const float y = acc[d] / l;
             if constexpr (OUT_MODE == 0)
-                reinterpret_cast<__half*>(out)[row * HD + d0 + d] = __float2half_rn(y);
+                reinterpret_cast<__half*>(out)[row * HD + t + 128 * d] = __float2half_rn(y);
             else
-                reinterpret_cast<float*>(out)[row * HD + d0 + d] = y;
+                reinterpret_cast<float*>(out)[row * HD + t + 128 * d] = y;
         }
     }
 }
@@ -439,7 +481,8 @@ int launch_reduce(const LaunchArgs& a)
 {
     const uint32_t n_splits = *(const uint32_t*)a.push;
     const size_t rows = a.groups[0];
-    if (rows == 0 || n_splits == 0) return fail_validation(a, "attn_reduce: groups[0] (rows) and n_splits must be > 0");
+    if (rows == 0 || n_splits == 0 || n_splits > (uint32_t)REDUCE_MAX_SPLITS)
+        return fail_validation(a, "attn_reduce: groups[0] (rows) must be > 0 and n_splits in 1..1024");
     if (int r = need_bytes(a, 0, rows * n_splits * (HD + 2) * 4, "part")) return r;
     const size_t out_bytes = OUT_MODE == 0 ? rows * HD * 2 : OUT_MODE == 1 ? rows * HD * 4 : rows * (HD + 2) * 4;
     if (int r = need_bytes(a, 1, out_bytes, "out")) return r;
@@ -459,7 +502,8 @@ int launch_combine_ranks_d128(const LaunchArgs& a)
 {
     const uint32_t n_ranks = *(const uint32_t*)a.push;
     const size_t rows = a.groups[0];
-    if (rows == 0 || n_ranks == 0) return fail_validation(a, "attn_combine_ranks: rows and n_ranks must be > 0");
+    if (rows == 0 || n_ranks == 0 || n_ranks > (uint32_t)REDUCE_MAX_SPLITS)
+        return fail_validation(a, "attn_combine_ranks: rows must be > 0 and n_ranks in 1..1024");
     if (int r = need_bytes(a, 0, rows * n_ranks * 130 * 4, "gathered partials")) return r;
     if (int r = need_bytes(a, 1, rows * 128 * 4, "out")) return r;
     reduce_kernel<128, 1><<<(uint32_t)rows, 128, 0, a.stream>>>((const float*)a.b[0].ptr, a.b[1].ptr, n_ranks, 1);

@@ -9,7 +9,7 @@
 //
 // One CTA = 64 query tokens x the 2 query heads of one kv head = 128 rows of S and O, so both
 // heads share every K/V tile (GQA grouping).  Per 64-key tile:
-//   TMA (128B swizzle, no multicast) -> smem K, V              loader warp
+//   TMA (128B swizzle, CTA-local) -> smem K, V                 loader warp
 //   S[128x64]  = Q K^T   tcgen05.mma kind::f16, D in TMEM      MMA warp, 8 instructions (K = 16 each)
 //   row softmax in registers: thread r owns TMEM lane r (tcgen05.ld 32x32b), base-2 exponent,
 //       running max raised only when it grows by > 2^8; masked tiles only at the band edges,

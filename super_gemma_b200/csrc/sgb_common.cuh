@@ -92,7 +92,7 @@ __device__ __forceinline__ bool mbar_wait(uint64_t* bar, uint32_t parity, uint32
     }
 }
 
-// ---- TMA (no multicast anywhere in this library) ------------------------------------------------
+// ---- TMA: every copy targets the issuing CTA only ---------------------------------------------
 __device__ __forceinline__ void tma_prefetch_desc(const CUtensorMap* m)
 {
     asm volatile("prefetch.tensormap [%0];" ::"l"(reinterpret_cast<uint64_t>(m)) : "memory");
