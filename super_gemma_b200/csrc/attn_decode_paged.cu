@@ -154,9 +154,10 @@ __global__ void __launch_bounds__(WPC * 32, MIN_CTAS)
     const uint32_t n_iter = active && n_stages > (uint32_t)sub ? (n_stages - sub + SUB - 1) / SUB : 0;
     __syncwarp();
 
+    const uint32_t page_shift = 31 - __clz(page);
     // Physical page of the stage with index `stage` (tokens 16*stage ..), checked, never followed blindly.
     auto lookup = [&](uint32_t stage) -> uint32_t {
-        const uint32_t lp = stage * STAGE_TOK / page;
+        const uint32_t lp = (stage * STAGE_TOK) >> page_shift;  // page is a power of two (checked on the host)
         uint32_t pp = 0;
         if (lp < table_len) {
             pp = __ldg(page_table + lp);
@@ -173,7 +174,7 @@ __global__ void __launch_bounds__(WPC * 32, MIN_CTAS)
     auto issue = [&](uint32_t it, uint32_t pp) {
         const int st = it % NSTAGES;
         const uint32_t tok0 = (s_begin + it * SUB) * STAGE_TOK;
-        const int row = (int)(pp * page + tok0 % page);
+        const int row = (int)((pp << page_shift) + (tok0 & (page - 1)));
         uint64_t* bar = &sm.full[warp][st];
         fence_proxy_async_smem();  // the slot's previous contents were read through the generic proxy
         mbar_arrive_expect_tx(bar, STAGE_BYTES);
@@ -520,7 +521,8 @@ int launch_decode_paged_q8kv_d128(const LaunchArgs& a)
     if (p.n_splits == 0 || a.groups[1] != p.n_splits)
         return fail_validation(a, "decode_paged: groups[1] must equal push.n_splits (> 0)");
     if (m_q > 4) return fail_validation(a, "decode_paged: at most 4 query tokens");
-    if (p.page == 0 || p.page % STAGE_TOK) return fail_validation(a, "decode_paged: page must be a multiple of 16 tokens");
+    if (p.page < (uint32_t)STAGE_TOK || (p.page & (p.page - 1)))
+        return fail_validation(a, "decode_paged: page must be a power of two, at least 16 tokens");
     const size_t row_bytes = (size_t)n_kv * HD;
     const size_t pool_rows = a.b[1].bytes / row_bytes;
     if (pool_rows == 0 || a.b[3].bytes / row_bytes != pool_rows)
@@ -616,7 +618,8 @@ extern "C" int sgb_decode_paged_q8kv_d128_noalloc(int device, void* stream, cons
     if (n_kv_heads == 0 || (n_kv_heads & 1)) return set_last_error(3, "decode_noalloc: n_kv_heads must be even and > 0");
     if (m_q == 0 || m_q > 4) return set_last_error(3, "decode_noalloc: m_q must be 1..4");
     if (kv_len == 0 || n_splits == 0) return set_last_error(3, "decode_noalloc: kv_len and n_splits must be > 0");
-    if (page == 0 || page % STAGE_TOK) return set_last_error(3, "decode_noalloc: page must be a multiple of 16 tokens");
+    if (page < (uint32_t)STAGE_TOK || (page & (page - 1)))
+        return set_last_error(3, "decode_noalloc: page must be a power of two, at least 16 tokens");
     const uint64_t part_rows = (uint64_t)m_q * n_kv_heads * G * n_splits;
     if (part_rows > NOALLOC_MAX_PART_ROWS) {
         char buf[200];

@@ -86,7 +86,7 @@ def test_error_variants(ctx):
     bufs = [ctx.new_buffer(64, np.uint8) for _ in range(8)]
     with pytest.raises(sg.Validation):  # odd number of kv heads
         ctx.dispatch(dec, bind(*bufs), (4, SCALE, 256), [3, 4, 1])
-    with pytest.raises(sg.Validation):  # page not a multiple of 64
+    with pytest.raises(sg.Validation):  # page not a power of two
         ctx.dispatch(dec, bind(*bufs), (4, SCALE, 100), [16, 4, 1])
     with pytest.raises(sg.State):
         import ctypes as C
