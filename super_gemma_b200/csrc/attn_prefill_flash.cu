@@ -207,9 +207,9 @@ __global__ void __launch_bounds__(FLASH_THREADS, 2) flash_prefill_kernel(const _
             for (int j = 0; j + 2 < n_tiles; ++j) {
                 const int b = j % KV_STAGES;
                 // K stage b is free once QK(j) has completed, V stage b once PV(j) has.
-                mbar_wait(&sm.s_ready[b], (j / 2) & 1, prm.status, 411, failed);
+                mbar_wait(&sm.s_ready[b], (j / 2) & 1, prm.status, 411, failed, 100);
                 load_k(j + 2);
-                mbar_wait(&sm.pv_done, j & 1, prm.status, 412, failed);
+                mbar_wait(&sm.pv_done, j & 1, prm.status, 412, failed, 100);
                 load_v(j + 2);
             }
         }
@@ -297,10 +297,11 @@ __global__ void __launch_bounds__(FLASH_THREADS, 2) flash_prefill_kernel(const _
                     if (pos < lo || pos > hi) v[j] = -INFINITY;
                 }
             }
-            // row max of the raw scores on four independent chains; scale2 > 0 commutes with max
+            // row max of the raw scores on four independent chains of three-input max; scale2 > 0
+            // commutes with max
             float mx4[4] = {v[0], v[1], v[2], v[3]};
 #pragma unroll
-            for (int j = 4; j < 64; j++) mx4[j & 3] = fmaxf(mx4[j & 3], v[j]);
+            for (int j = 4; j < 64; j += 2) mx4[(j >> 1) & 3] = max3(mx4[(j >> 1) & 3], v[j], v[j + 1]);
             const float mx = fmaxf(fmaxf(mx4[0], mx4[1]), fmaxf(mx4[2], mx4[3])) * scale2;
             const bool grow = mx > m_run + RESCALE_T;
             float corr = 1.0f;
@@ -309,16 +310,18 @@ __global__ void __launch_bounds__(FLASH_THREADS, 2) flash_prefill_kernel(const _
                 m_run = mx;
                 l_run *= corr;
             }
-            const float neg_m = -m_run;
+            // p = 2^(s * scale2 - m) with the multiply-add and the running sums on packed f32x2 pipes
+            const float2 sc2 = make_float2(scale2, scale2), neg_m = make_float2(-m_run, -m_run);
             uint32_t pk[32];
-            float ls4[4] = {0.0f, 0.0f, 0.0f, 0.0f};
+            float2 ls4[4] = {make_float2(0.0f, 0.0f), make_float2(0.0f, 0.0f), make_float2(0.0f, 0.0f), make_float2(0.0f, 0.0f)};
 #pragma unroll
             for (int j = 0; j < 32; j++) {
-                const float p0 = ex2(fmaf(v[2 * j], scale2, neg_m)), p1 = ex2(fmaf(v[2 * j + 1], scale2, neg_m));
-                ls4[j & 3] += p0 + p1;  // l in f32 from the unrounded p (attn_prefill_global_flash_sp.wgsl:147-156)
-                pk[j] = pack_half2(p0, p1);
+                const float2 x = __ffma2_rn(make_float2(v[2 * j], v[2 * j + 1]), sc2, neg_m);
+                const float2 pp = make_float2(ex2(x.x), ex2(x.y));
+                ls4[j & 3] = __fadd2_rn(ls4[j & 3], pp);  // l in f32 from the unrounded p (attn_prefill_global_flash_sp.wgsl:147-156)
+                pk[j] = pack_half2(pp.x, pp.y);
             }
-            l_run += (ls4[0] + ls4[1]) + (ls4[2] + ls4[3]);
+            l_run += ((ls4[0].x + ls4[0].y) + (ls4[1].x + ls4[1].y)) + ((ls4[2].x + ls4[2].y) + (ls4[3].x + ls4[3].y));
 
             // P's buffer and O are only touched once PV of the previous tile has completed.
             if (it > 0) {

@@ -77,12 +77,16 @@ __device__ __forceinline__ bool mbar_try_wait(uint64_t* bar, uint32_t parity)
 // that a broken pipeline drains in one bound, not one bound per stage.
 constexpr long long WAIT_LIMIT_CYCLES = 2000000000LL;
 
-__device__ __forceinline__ bool mbar_wait(uint64_t* bar, uint32_t parity, uint32_t* status, uint32_t site, bool& failed)
+// backoff_ns > 0 makes a waiter that is not latency-critical sleep between polls, leaving the issue
+// slots to the warps that do the arithmetic.
+__device__ __forceinline__ bool mbar_wait(uint64_t* bar, uint32_t parity, uint32_t* status, uint32_t site, bool& failed,
+                                          uint32_t backoff_ns = 0)
 {
     if (failed) return false;
     if (mbar_try_wait(bar, parity)) return true;
     const long long t0 = clock64();
     for (;;) {
+        if (backoff_ns) __nanosleep(backoff_ns);
         if (mbar_try_wait(bar, parity)) return true;
         if (clock64() - t0 > WAIT_LIMIT_CYCLES) {
             failed = true;
@@ -205,6 +209,13 @@ __device__ __forceinline__ float ex2(float x)
     float y;
     asm("ex2.approx.ftz.f32 %0, %1;" : "=f"(y) : "f"(x));
     return y;
+}
+// Three-input maximum (one instruction on sm_100).
+__device__ __forceinline__ float max3(float a, float b, float c)
+{
+    float d;
+    asm("max.f32 %0, %1, %2, %3;" : "=f"(d) : "f"(a), "f"(b), "f"(c));
+    return d;
 }
 __device__ __forceinline__ uint32_t pack_half2(float lo, float hi)
 {
