@@ -342,6 +342,7 @@ def cpu_prefill_sample(m, ctx_len, target_s, seed=SEED):
     rows of the headline workload and returns TFLOP/s over the sampled rows."""
     from oracle import sg_oracle as O
 
+    O.set_threads(len(os.sched_getaffinity(0)))  # all host cores this process may use, whatever OMP_NUM_THREADS says
     q0 = ctx_len - m
     rng = np.random.default_rng(seed)
     n_kv = KV

@@ -561,6 +561,16 @@ void sgo_prefill_flash_f32(const uint16_t *q_f16, const sgo_kv_src *ks, const sg
     }
 }
 
+/* Launchers such as torchrun export OMP_NUM_THREADS=1; the timed baseline asks for what it wants. */
+void sgo_set_threads(int n)
+{
+#ifdef _OPENMP
+    if (n > 0) omp_set_num_threads(n);
+#else
+    (void)n;
+#endif
+}
+
 int sgo_num_threads(void)
 {
 #ifdef _OPENMP

@@ -81,6 +81,7 @@ def lib() -> C.CDLL:
         L.sgo_prefill_flash_f32.argtypes = [vp, C.POINTER(_KvSrc), C.POINTER(_KvSrc), vp, sz, u32, i32, i32, i32, u32, f32,
                                             u32, vp, sz]
         L.sgo_num_threads.restype = i32
+        L.sgo_set_threads.argtypes = [i32]
         _lib = L
     return _lib
 
@@ -99,6 +100,10 @@ def _c(a, dtype) -> np.ndarray:
 
 def num_threads() -> int:
     return lib().sgo_num_threads()
+
+
+def set_threads(n: int) -> None:
+    lib().sgo_set_threads(n)
 
 
 # ---- f16 -----------------------------------------------------------------------------------
