@@ -244,9 +244,9 @@ __global__ void __launch_bounds__(FLASH_THREADS, 2) flash_prefill_kernel(const _
                 tc_fence_after_sync();
 #pragma unroll
                 for (int kk = 0; kk < 4; kk++) {
-                    const uint64_t da = umma_desc_sw128(smem_u32(sm.p) + kk * 32, 16, 1024);
+                    // P(j) lives in the first 32 columns of S[b] (packed f16 pairs), written by the softmax warps
                     const uint64_t db = umma_desc_sw128(smem_u32(sm.v[b][0]) + kk * 2048, HALF_TILE, 1024);
-                    umma_f16_ss(tmem + TMEM_O, da, db, IDESC_PV, (j | kk) ? 1u : 0u);
+                    umma_f16_ts(tmem + TMEM_O, tmem + TMEM_S + b * BLOCK_N + kk * 8, db, IDESC_PV, (j | kk) ? 1u : 0u);
                 }
                 umma_commit(&sm.pv_done);
                 if (j + 2 < n_tiles) {
@@ -340,14 +340,11 @@ __global__ void __launch_bounds__(FLASH_THREADS, 2) flash_prefill_kernel(const _
                     tc_wait_st();
                 }
             }
-            // P row r, 16-byte chunk c (keys 8c..8c+7) sits at chunk c ^ (r & 7) of its 128-byte row.
-            {
-                uint8_t* prow = sm.p + r * 128;
-#pragma unroll
-                for (int c = 0; c < 8; c++)
-                    *reinterpret_cast<uint4*>(prow + ((c ^ (r & 7)) << 4)) = make_uint4(pk[4 * c], pk[4 * c + 1], pk[4 * c + 2], pk[4 * c + 3]);
-            }
-            fence_proxy_async_smem();
+            // P row r goes back into tensor memory over the first half of S[b] (this thread has S in
+            // registers; Q K^T of tile it + 2 overwrites the buffer only after P V of this tile, because the
+            // tensor pipe runs in order).
+            tmem_st_32x32b_x32(lane_addr + TMEM_S + b * BLOCK_N, pk);
+            tc_wait_st();
             tc_fence_before_sync();
             mbar_arrive(&sm.p_ready);
         }
