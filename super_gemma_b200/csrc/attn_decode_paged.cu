@@ -170,18 +170,27 @@ __global__ void __launch_bounds__(WPC * 32, MIN_CTAS)
         }
         return pp;
     };
-    // Lane 0 only: start the four TMA copies of iteration `it` into slot it % NSTAGES.
+    // Lanes 0..3 start the four TMA copies of iteration `it` into slot it % NSTAGES with ONE instruction:
+    // lane 0 = K quants, 1 = K scales, 2 = V quants, 3 = V scales (all four are 3-D copies).
+    const CUtensorMap* my_map = lane == 0 ? &tm_kq : lane == 1 ? &tm_ks : lane == 2 ? &tm_vq : &tm_vs;
+    const uint32_t my_dst0 = lane == 0 ? smem_u32(sm.kq[warp][0]) : lane == 1 ? smem_u32(sm.ks[warp][0])
+                           : lane == 2 ? smem_u32(sm.vq[warp][0]) : smem_u32(sm.vs[warp][0]);
+    const uint32_t my_stride = (lane & 1) ? SCALE_TILE : HEAD_TILE;
+    const int my_c1 = (lane & 1) ? (kvh >> 1) : kvh;
+    const uint32_t bar0 = smem_u32(&sm.full[warp][0]);
     auto issue = [&](uint32_t it, uint32_t pp) {
-        const int st = it % NSTAGES;
+        const uint32_t st = it % NSTAGES;
         const uint32_t tok0 = (s_begin + it * SUB) * STAGE_TOK;
         const int row = (int)((pp << page_shift) + (tok0 & (page - 1)));
-        uint64_t* bar = &sm.full[warp][st];
-        fence_proxy_async_smem();  // the slot's previous contents were read through the generic proxy
-        mbar_arrive_expect_tx(bar, STAGE_BYTES);
-        tma_load_3d(sm.kq[warp][st], &tm_kq, bar, 0, kvh, row);
-        tma_load_2d(sm.ks[warp][st], &tm_ks, bar, (kvh >> 1) * 8, row);
-        tma_load_3d(sm.vq[warp][st], &tm_vq, bar, 0, kvh, row);
-        tma_load_2d(sm.vs[warp][st], &tm_vs, bar, (kvh >> 1) * 8, row);
+        const uint32_t bar = bar0 + st * 8;
+        if (lane == 0) {
+            fence_proxy_async_smem();  // the slot's previous contents were read through the generic proxy
+            asm volatile("mbarrier.arrive.expect_tx.shared::cta.b64 _, [%0], %1;" ::"r"(bar), "r"(STAGE_BYTES) : "memory");
+        }
+        asm volatile(
+            "cp.async.bulk.tensor.3d.shared::cluster.global.mbarrier::complete_tx::bytes [%0], [%1, {%3, %4, %5}], [%2];"
+            ::"r"(my_dst0 + st * my_stride), "l"(reinterpret_cast<uint64_t>(my_map)), "r"(bar), "r"(0), "r"(my_c1), "r"(row)
+            : "memory");
     };
     // Start the pipeline before anything else: lanes 0..NSTAGES-1 fetch the first page entries side
     // by side (one memory latency, not NSTAGES), lane 0 issues; the Q loads below overlap the copies.
@@ -191,13 +200,13 @@ __global__ void __launch_bounds__(WPC * 32, MIN_CTAS)
         if ((uint32_t)lane < n_pre) my_pp = lookup(s_begin + lane * SUB);
         for (uint32_t it = 0; it < n_pre; ++it) {
             const uint32_t pp = __shfl_sync(0xffffffffu, my_pp, it);
-            if (lane == 0) issue(it, pp);
+            if (lane < 4) issue(it, pp);
         }
     }
     // The page of the next stage to be issued is looked up one iteration early, so the load's
     // latency is covered by a tile of work.
     uint32_t next_pp = 0;
-    if (n_iter > (uint32_t)NSTAGES && lane == 0) next_pp = lookup(s_begin + NSTAGES * SUB);
+    if (n_iter > (uint32_t)NSTAGES && lane < 4) next_pp = lookup(s_begin + NSTAGES * SUB);
 
     // MMA roles.  QK^T: A = K (16 tokens x 16 dims of chunk c), B = Q^T (16 dims x 8 query rows).
     //            PV  : A = V^T (16 dims of chunk c x 16 tokens), B = P'^T (16 tokens x 8 query rows).
@@ -365,7 +374,7 @@ __global__ void __launch_bounds__(WPC * 32, MIN_CTAS)
 
         // Refill this slot for iteration it + NSTAGES; every lane is done reading it.
         __syncwarp();
-        if (lane == 0 && it + NSTAGES < n_iter) {
+        if (lane < 4 && it + NSTAGES < n_iter) {
             issue(it + NSTAGES, next_pp);
             if (it + NSTAGES + 1 < n_iter) next_pp = lookup(s_begin + (it + NSTAGES + 1) * SUB);
         }
@@ -454,10 +463,10 @@ int encode_pool_maps(const LaunchArgs& a, CUtensorMap (&tm)[4], const void* cons
         const uint64_t qs[2] = {HD, (uint64_t)n_kv * HD};
         const uint32_t qb[3] = {HD, 1, STAGE_TOK};
         if (int r = encode_tensor_map(a, &tm[2 * i], 0, 3, const_cast<void*>(quants[i]), qd, qs, qb, 3)) return r;
-        const uint64_t sd[2] = {(uint64_t)n_kv * 4, pool_rows};
-        const uint64_t ss[1] = {(uint64_t)n_kv * 8};
-        const uint32_t sb[2] = {8, STAGE_TOK};
-        if (int r = encode_tensor_map(a, &tm[2 * i + 1], 1, 2, const_cast<void*>(scales[i]), sd, ss, sb, 0)) return r;
+        const uint64_t sd[3] = {8, (uint64_t)n_kv / 2, pool_rows};
+        const uint64_t ss[2] = {16, (uint64_t)n_kv * 8};
+        const uint32_t sb[3] = {8, 1, STAGE_TOK};
+        if (int r = encode_tensor_map(a, &tm[2 * i + 1], 1, 3, const_cast<void*>(scales[i]), sd, ss, sb, 0)) return r;
     }
     return 0;
 }
