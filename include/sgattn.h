@@ -128,6 +128,37 @@ int sgb_timer_stamp(sgb_ctx *ctx, sgb_timer *t, uint32_t index); /* also legal w
 int sgb_timer_read_ns(sgb_timer *t, uint64_t *out_ns, uint32_t n); /* ns since stamp 0; syncs the events */
 void sgb_timer_destroy(sgb_timer *t);
 
+/* ---- cache2 page tables: the radix trie of docs/plans/04-kv-cache.md:40-51 and the page-size ---- */
+/* constants of crates/sg-cache/src/lib.rs:9-13 (the reference has the design only, no code).     */
+/* Host-side and device-free: a trie keyed by whole pages of token ids over a pool of `pool_pages` */
+/* physical KV pages of `page_tokens` tokens (a power of two in 16..512).  It produces the        */
+/* page_table the paged kernels read; the caller uploads it with sgb_buffer_upload.  Single        */
+/* writer, like the reference's design: calls on one handle must not overlap.                      */
+typedef struct sgb_cache2 sgb_cache2;
+typedef struct sgb_cache2_stats_t {
+    uint32_t page_tokens, pool_pages, free_pages, reclaimable_pages, live_sequences, reserved;
+    uint64_t hits, misses, evictions;
+} sgb_cache2_stats_t;
+int sgb_cache2_create(uint32_t page_tokens, uint32_t pool_pages, sgb_cache2 **out);
+void sgb_cache2_destroy(sgb_cache2 *c);
+/* Longest cached page-aligned prefix of `tokens`, in tokens (04-kv-cache.md:46). No state change. */
+int sgb_cache2_lookup(sgb_cache2 *c, const int32_t *tokens, uint64_t n_tokens, uint64_t *matched_tokens);
+/* Start a sequence that knows `n_tokens` token ids and may grow to `capacity_tokens`: the pages of
+ * its longest cached prefix are shared (their K/V is already in the pool: the caller appends from
+ * token `*reused_tokens` on), private pages are taken for the rest -- from the free list, else by
+ * reclaiming least-recently-used cached pages that no live sequence holds.  Writes the logical ->
+ * physical page list to table[0..*n_pages) and a handle to *seq.  SGB_ERR_STATE and no change when
+ * the pool cannot supply the pages; SGB_ERR_VALIDATION when table_capacity is too small. */
+int sgb_cache2_acquire(sgb_cache2 *c, const int32_t *tokens, uint64_t n_tokens, uint64_t capacity_tokens, uint32_t *table,
+                       uint32_t table_capacity, uint32_t *n_pages, uint64_t *reused_tokens, uint64_t *seq);
+/* Insert on commit (04-kv-cache.md:47-48): the sequence's private pages that tokens[0..n_tokens)
+ * fill completely become shareable trie nodes (the sequence keeps holding them).  Call it once their
+ * K/V is in the pool.  The physical page list of the sequence does not change. */
+int sgb_cache2_commit(sgb_cache2 *c, uint64_t seq, const int32_t *tokens, uint64_t n_tokens);
+/* End a sequence: private pages go back to the free list, shared ones stay cached until reclaimed. */
+int sgb_cache2_release(sgb_cache2 *c, uint64_t seq);
+int sgb_cache2_stats(const sgb_cache2 *c, sgb_cache2_stats_t *out);
+
 /* ---- allocation-free decode (no counterpart in the reference) ---------------------------------- */
 /* For hosts that cannot allocate device memory when they need attention -- a serving process that
  * has given all of HBM to its KV pool, or a caller inside a phase where cudaMalloc is off limits.

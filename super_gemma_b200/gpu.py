@@ -72,6 +72,12 @@ class _Binding(C.Structure):
     _fields_ = [("index", C.c_uint32), ("buffer", C.c_void_p)]
 
 
+class _Cache2Stats(C.Structure):
+    _fields_ = [("page_tokens", C.c_uint32), ("pool_pages", C.c_uint32), ("free_pages", C.c_uint32),
+                ("reclaimable_pages", C.c_uint32), ("live_sequences", C.c_uint32), ("reserved", C.c_uint32),
+                ("hits", C.c_uint64), ("misses", C.c_uint64), ("evictions", C.c_uint64)]
+
+
 # Every symbol include/sgattn.h declares: (restype, argtypes).
 _vp, _u32, _u64, _sz, _int = C.c_void_p, C.c_uint32, C.c_uint64, C.c_size_t, C.c_int
 _PP = C.POINTER(C.c_void_p)
@@ -115,6 +121,13 @@ ABI = {
     "sgb_timer_stamp": (_int, [_vp, _vp, _u32]),
     "sgb_timer_read_ns": (_int, [_vp, C.POINTER(_u64), _u32]),
     "sgb_timer_destroy": (None, [_vp]),
+    "sgb_cache2_create": (_int, [_u32, _u32, _PP]),
+    "sgb_cache2_destroy": (None, [_vp]),
+    "sgb_cache2_lookup": (_int, [_vp, _vp, _u64, C.POINTER(_u64)]),
+    "sgb_cache2_acquire": (_int, [_vp, _vp, _u64, _u64, _vp, _u32, C.POINTER(_u32), C.POINTER(_u64), C.POINTER(_u64)]),
+    "sgb_cache2_commit": (_int, [_vp, _u64, _vp, _u64]),
+    "sgb_cache2_release": (_int, [_vp, _u64]),
+    "sgb_cache2_stats": (_int, [_vp, C.POINTER(_Cache2Stats)]),
     "sgb_decode_paged_q8kv_d128_noalloc": (_int, [_int, _vp, _vp, _vp, _vp, _vp, _vp, _vp, _u32, _u64, _vp, _vp, _u32, _u32, _u32,
                                                    _u32, _u32, C.c_float]),
 }
