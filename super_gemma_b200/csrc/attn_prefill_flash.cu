@@ -14,11 +14,15 @@
 //   row softmax in registers: thread r owns TMEM lane r (tcgen05.ld 32x32b), base-2 exponent,
 //       running max raised only when it grows by > 2^8; masked tiles only at the band edges,
 //       tiles wholly outside [qpos+1-window, qpos] are never visited           4 softmax warps
-//   P -> smem as f16 in the K-major swizzled layout, fence.proxy.async
-//   O[128x128] += P V    tcgen05.mma, V as the MN-major B operand straight from its [key][dim] tile
+//   P -> back into tensor memory over S as packed f16 pairs (tcgen05.st)
+//   O[128x128] += P V    tcgen05.mma with A = P from tensor memory, V as the MN-major B operand straight
+//                        from its [key][dim] tile
 // S is double-buffered in TMEM and the three roles talk through mbarriers only, so Q K^T of the
 // next tile and P V of the previous one run while the softmax warps work.  Two CTAs fit per SM
 // (112 KB smem, 256 TMEM columns each).  Every mbarrier wait is bounded; TMEM is always freed.
+#include <cmath>
+#include <cstdlib>
+
 #include "sgb_common.cuh"
 #include "sgb_kernels.h"
 
@@ -59,10 +63,13 @@ struct FlashSmem {
     uint64_t s_ready[2];                     // MMA commit: S[b] holds Q K^T of a tile
     uint64_t s_free[2];                      // 128 softmax threads: S[b] has been read
     uint64_t q_bar;
-    uint64_t p_ready;                        // 128 softmax threads: P is in shared memory
-    uint64_t pv_done;                        // MMA commit: O += P V of a tile has completed
+    // p_ready and pv_done are indexed by tile parity like S: a producer can then never be two phases
+    // ahead of a consumer that has not polled yet, whatever the relative speed of the roles.
+    uint64_t p_ready[2];                     // 128 softmax threads: P(j) is in tensor memory
+    uint64_t pv_done[2];                     // MMA commit: O += P V of a tile has completed
     uint32_t tmem_base;
-    uint32_t pad[9];
+    uint32_t abort;                          // a bounded wait ran out somewhere in the CTA
+    uint32_t pad[4];
 };
 static_assert(sizeof(FlashSmem) == 7 * 2 * HALF_TILE + 128, "tiles + barriers, no padding");
 static_assert(2 * (sizeof(FlashSmem) + 1024) <= 228 * 1024, "two CTAs per SM");
@@ -70,6 +77,8 @@ static_assert(2 * (sizeof(FlashSmem) + 1024) <= 228 * 1024, "two CTAs per SM");
 struct FlashParams {
     const uint32_t* step;
     float* out;
+    float* part_acc;     // pieces > 1: [row][piece][128] unnormalised O
+    float* part_ml;      // pieces > 1: [row][piece][2] = running max (base-2 exponent units), sum
     uint32_t* status;
     uint32_t m_tokens;   // query tokens in the chunk
     uint32_t n_kv;
@@ -133,8 +142,15 @@ __global__ void __launch_bounds__(FLASH_THREADS, 2) flash_prefill_kernel(const _
         n_hist = (int)(last_qpos / BLOCK_N - band_lo / BLOCK_N + 1);
         n_tiles = n_hist;
     }
+    // gridDim.z pieces share a unit: piece z visits a contiguous run of its key tiles and leaves a partial
+    // (unnormalised O, max, sum) that combine_pieces_kernel merges.  `it` below counts from the piece's
+    // first tile, so barrier phases do not depend on the split.
+    const int per_piece = (n_tiles + (int)gridDim.z - 1) / (int)gridDim.z;
+    const int t_begin = min(n_tiles, (int)blockIdx.z * per_piece);
+    n_tiles = min(n_tiles, t_begin + per_piece) - t_begin;
     auto tile_at = [&](int it) {
         Tile t;
+        it += t_begin;
         if (it < n_hist) {
             t.src = 0;
             t.pos0 = hist_pos0 + (int64_t)it * BLOCK_N;
@@ -159,10 +175,11 @@ __global__ void __launch_bounds__(FLASH_THREADS, 2) flash_prefill_kernel(const _
             mbar_init(&sm.full_v[i], 1);
             mbar_init(&sm.s_ready[i], 1);
             mbar_init(&sm.s_free[i], SOFTMAX_THREADS);
+            mbar_init(&sm.p_ready[i], SOFTMAX_THREADS);
+            mbar_init(&sm.pv_done[i], 1);
         }
         mbar_init(&sm.q_bar, 1);
-        mbar_init(&sm.p_ready, SOFTMAX_THREADS);
-        mbar_init(&sm.pv_done, 1);
+        sm.abort = 0;
         mbar_fence_init();
     }
     if (warp == 0) {
@@ -200,16 +217,18 @@ __global__ void __launch_bounds__(FLASH_THREADS, 2) flash_prefill_kernel(const _
             mbar_arrive_expect_tx(&sm.q_bar, Q_BYTES);
             tma_load_3d(sm.q[0], &tm_q, &sm.q_bar, 0, kvh * G, (int)m0);
             tma_load_3d(sm.q[1], &tm_q, &sm.q_bar, 64, kvh * G, (int)m0);
-            load_k(0);
+            if (n_tiles > 0) load_k(0);
             if (n_tiles > 1) load_k(1);
-            load_v(0);
+            if (n_tiles > 0) load_v(0);
             if (n_tiles > 1) load_v(1);
             for (int j = 0; j + 2 < n_tiles; ++j) {
                 const int b = j % KV_STAGES;
                 // K stage b is free once QK(j) has completed, V stage b once PV(j) has.
                 mbar_wait(&sm.s_ready[b], (j / 2) & 1, prm.status, 411, failed, 100);
+                if (failed) break;  // never write into a stage that may still be read
                 load_k(j + 2);
-                mbar_wait(&sm.pv_done, j & 1, prm.status, 412, failed, 100);
+                mbar_wait(&sm.pv_done[b], (j / 2) & 1, prm.status, 412, failed, 100);
+                if (failed) break;
                 load_v(j + 2);
             }
         }
@@ -222,6 +241,7 @@ __global__ void __launch_bounds__(FLASH_THREADS, 2) flash_prefill_kernel(const _
             auto issue_qk = [&](int j) {
                 const int b = j % KV_STAGES;
                 mbar_wait(&sm.full_k[b], (j / KV_STAGES) & 1, prm.status, 402, failed);
+                if (failed) return;
                 tc_fence_after_sync();
 #pragma unroll
                 for (int h = 0; h < 2; h++) {
@@ -235,12 +255,13 @@ __global__ void __launch_bounds__(FLASH_THREADS, 2) flash_prefill_kernel(const _
                 umma_commit(&sm.s_ready[b]);
             };
             mbar_wait(&sm.q_bar, 0, prm.status, 401, failed);
-            issue_qk(0);
+            if (n_tiles > 0) issue_qk(0);
             if (n_tiles > 1) issue_qk(1);
             for (int j = 0; j < n_tiles; ++j) {
                 const int b = j % KV_STAGES;
-                mbar_wait(&sm.p_ready, j & 1, prm.status, 403, failed);
+                mbar_wait(&sm.p_ready[b], (j / 2) & 1, prm.status, 403, failed);
                 mbar_wait(&sm.full_v[b], (j / KV_STAGES) & 1, prm.status, 405, failed);
+                if (failed) break;
                 tc_fence_after_sync();
 #pragma unroll
                 for (int kk = 0; kk < 4; kk++) {
@@ -248,10 +269,11 @@ __global__ void __launch_bounds__(FLASH_THREADS, 2) flash_prefill_kernel(const _
                     const uint64_t db = umma_desc_sw128(smem_u32(sm.v[b][0]) + kk * 2048, HALF_TILE, 1024);
                     umma_f16_ts(tmem + TMEM_O, tmem + TMEM_S + b * BLOCK_N + kk * 8, db, IDESC_PV, (j | kk) ? 1u : 0u);
                 }
-                umma_commit(&sm.pv_done);
+                umma_commit(&sm.pv_done[b]);
                 if (j + 2 < n_tiles) {
                     // S[b] was read by the softmax warps before they produced P(j).
                     mbar_wait(&sm.s_free[b], (j / 2) & 1, prm.status, 406, failed);
+                    if (failed) break;
                     issue_qk(j + 2);
                 }
             }
@@ -323,11 +345,15 @@ __global__ void __launch_bounds__(FLASH_THREADS, 2) flash_prefill_kernel(const _
             }
             l_run += ((ls4[0].x + ls4[0].y) + (ls4[1].x + ls4[1].y)) + ((ls4[2].x + ls4[2].y) + (ls4[3].x + ls4[3].y));
 
-            // P's buffer and O are only touched once PV of the previous tile has completed.
-            if (it > 0) {
-                mbar_wait(&sm.pv_done, (it - 1) & 1, prm.status, 407, failed);
+            // O is rescaled where a row's max moved (rare after the first tiles), and only once P V of the
+            // previous tile has completed.  P(it) itself needs no such wait: it goes into S[b], which the
+            // tensor pipe next touches with P V(it).  (Most tiles skip this wait; its parity stays
+            // unambiguous because pv_done[b ^ 1] is next committed by P V(it + 1), which needs this
+            // thread's P(it + 1).)
+            if (it > 0 && __any_sync(0xffffffffu, grow)) {
+                mbar_wait(&sm.pv_done[b ^ 1], ((it - 1) / 2) & 1, prm.status, 407, failed);
                 tc_fence_after_sync();
-                if (__any_sync(0xffffffffu, grow)) {  // rescale O where a row's max moved
+                {
 #pragma unroll
                     for (int c = 0; c < 4; c++) {
                         uint32_t o[32];
@@ -346,33 +372,117 @@ __global__ void __launch_bounds__(FLASH_THREADS, 2) flash_prefill_kernel(const _
             tmem_st_32x32b_x32(lane_addr + TMEM_S + b * BLOCK_N, pk);
             tc_wait_st();
             tc_fence_before_sync();
-            mbar_arrive(&sm.p_ready);
+            mbar_arrive(&sm.p_ready[b]);
         }
-        mbar_wait(&sm.pv_done, (n_tiles - 1) & 1, prm.status, 408, failed);
+        // the tensor pipe completes in order: the last P V done means all of them are
+        if (n_tiles > 0) mbar_wait(&sm.pv_done[(n_tiles - 1) & 1], ((n_tiles - 1) / 2) & 1, prm.status, 408, failed);
         tc_fence_after_sync();
 
-        // ---- epilogue: out = O / l.  The TMEM loads are warp-wide, so every thread takes part and only
-        // the stores are predicated (rows past the end of the chunk are not written). ---------------------
+        // ---- epilogue: out = O / l, or this piece's partial.  The TMEM loads are warp-wide, so every thread
+        // takes part and only the stores are predicated (rows past the end of the chunk are not written). ----
         const bool live = (uint32_t)(r >> 1) < tok_in_tile;
-        const float inv_l = 1.0f / l_run;
-        float* orow = prm.out + ((size_t)(live ? tok : m0) * (prm.n_kv * G) + kvh * G + (r & 1)) * HD;
+        const size_t row = (size_t)(live ? tok : m0) * (prm.n_kv * G) + kvh * G + (r & 1);
+        const bool whole = gridDim.z == 1;
+        const float mul = whole ? 1.0f / l_run : 1.0f;
+        float* orow = whole ? prm.out + row * HD : prm.part_acc + (row * gridDim.z + blockIdx.z) * HD;
+        if (!whole && live) *reinterpret_cast<float2*>(prm.part_ml + (row * gridDim.z + blockIdx.z) * 2) = make_float2(m_run, l_run);
 #pragma unroll
         for (int c = 0; c < 4; c++) {
             uint32_t o[32];
-            tmem_ld_32x32b_x32(lane_addr + TMEM_O + 32 * c, o);
-            tc_wait_ld();
+            if (n_tiles > 0) {  // uniform over the CTA
+                tmem_ld_32x32b_x32(lane_addr + TMEM_O + 32 * c, o);
+                tc_wait_ld();
+            } else {
+#pragma unroll
+                for (int j = 0; j < 32; j++) o[j] = 0u;  // an empty piece: m = sentinel, l = 0, O = 0
+            }
             if (live) {
 #pragma unroll
                 for (int j = 0; j < 8; j++)
                     *reinterpret_cast<float4*>(orow + 32 * c + 4 * j) =
-                        make_float4(__uint_as_float(o[4 * j]) * inv_l, __uint_as_float(o[4 * j + 1]) * inv_l,
-                                    __uint_as_float(o[4 * j + 2]) * inv_l, __uint_as_float(o[4 * j + 3]) * inv_l);
+                        make_float4(__uint_as_float(o[4 * j]) * mul, __uint_as_float(o[4 * j + 1]) * mul,
+                                    __uint_as_float(o[4 * j + 2]) * mul, __uint_as_float(o[4 * j + 3]) * mul);
             }
         }
     }
+    // A wait that ran out leaves copies and MMAs of this CTA in flight that nobody will wait for: give them
+    // a bounded time to land before the shared and tensor memory they target is handed to the next CTA.
+    if (failed) sm.abort = 1;
     tc_fence_before_sync();
     __syncthreads();
+    if (*(volatile uint32_t*)&sm.abort != 0u) {
+        for (int i = 0; i < 50; i++) __nanosleep(1000);
+        __syncthreads();
+    }
     if (warp == 0) tmem_dealloc(tmem, TMEM_COLS);
+}
+
+// Merge the pieces of every row: out = sum_p 2^(m_p - M) O_p / sum_p 2^(m_p - M) l_p, pieces in index
+// order (fixed order => bit-identical reruns).  One warp per row, lane = 4 dims.
+constexpr int MAX_PIECES = 16;
+__global__ void __launch_bounds__(256) combine_pieces_kernel(const float* __restrict__ part_acc, const float* __restrict__ part_ml,
+                                                             float* __restrict__ out, uint32_t rows, uint32_t pieces)
+{
+    const uint32_t row = blockIdx.x * 8 + (threadIdx.x >> 5), lane = threadIdx.x & 31;
+    if (row >= rows) return;
+    float m[MAX_PIECES], l[MAX_PIECES];
+    float big = NEG_SENTINEL;
+#pragma unroll
+    for (int p = 0; p < MAX_PIECES; p++) {
+        if (p < (int)pieces) {
+            const float2 ml = *reinterpret_cast<const float2*>(part_ml + ((size_t)row * pieces + p) * 2);
+            m[p] = ml.x;
+            l[p] = ml.y;
+            big = fmaxf(big, ml.x);
+        }
+    }
+    float4 acc = make_float4(0.0f, 0.0f, 0.0f, 0.0f);
+    float den = 0.0f;
+#pragma unroll
+    for (int p = 0; p < MAX_PIECES; p++) {
+        if (p < (int)pieces) {
+            const float w = l[p] > 0.0f ? ex2(m[p] - big) : 0.0f;
+            const float4 a = *reinterpret_cast<const float4*>(part_acc + ((size_t)row * pieces + p) * HD + lane * 4);
+            acc.x = fmaf(w, a.x, acc.x);
+            acc.y = fmaf(w, a.y, acc.y);
+            acc.z = fmaf(w, a.z, acc.z);
+            acc.w = fmaf(w, a.w, acc.w);
+            den = fmaf(w, l[p], den);
+        }
+    }
+    const float inv = 1.0f / den;
+    *reinterpret_cast<float4*>(out + (size_t)row * HD + lane * 4) = make_float4(acc.x * inv, acc.y * inv, acc.z * inv, acc.w * inv);
+}
+
+// Scratch for the pieces, one growing allocation per device, made outside stream capture only.
+struct PieceScratch {
+    float* ptr = nullptr;
+    size_t bytes = 0;
+};
+PieceScratch g_piece_scratch[64];
+
+// How many pieces to cut every unit's key range into.  The host does not know kv_len (it lives in the
+// step buffer), so the choice rests on the grid alone: with `units` equal CTAs on `slots` resident
+// places the last wave is ceil(w) - w empty; more pieces make the waves finer.  The K buffer's row
+// count bounds kv_len from above and keeps tiny problems whole.
+int choose_pieces(size_t units, int slots, size_t kv_rows_bound)
+{
+    if (const char* e = getenv("SGB_FLASH_PIECES")) {
+        const int v = atoi(e);
+        if (v >= 1 && v <= MAX_PIECES) return v;
+    }
+    const size_t max_by_len = kv_rows_bound / (32 * BLOCK_N);  // at least 32 tiles per piece
+    int best = 1;
+    double best_eff = 0.0;
+    for (int p = 1; p <= MAX_PIECES && (p == 1 || (size_t)p <= max_by_len); p++) {
+        const double w = (double)units * p / slots;
+        const double eff = w / ceil(w) - 0.004 * (p - 1);  // each extra piece costs a partial write + read
+        if (eff > best_eff + 1e-9) {
+            best_eff = eff;
+            best = p;
+        }
+    }
+    return best;
 }
 
 struct PushScaleWindow {
@@ -432,11 +542,52 @@ int run_flash(const LaunchArgs& a, const BufView& q, const BufView& k0, const Bu
             return r;
         attr_set[TWO_SRC][a.device] = true;
     }
-    FlashParams prm{(const uint32_t*)step.ptr, (float*)out.ptr, a.status, m_tokens, n_kv, window, ring, scale};
-    const dim3 grid((m_tokens + BLOCK_TOK - 1) / BLOCK_TOK, n_kv);
+    const uint32_t q_tiles = (m_tokens + BLOCK_TOK - 1) / BLOCK_TOK;
+    const size_t rows = (size_t)m_tokens * n_q;
+    int pieces = TWO_SRC ? 1 : choose_pieces((size_t)q_tiles * n_kv, 2 * a.sm_count, k0.bytes / ((size_t)n_kv * HD * 2));
+    float* part_acc = nullptr;
+    float* part_ml = nullptr;
+    if (pieces > 1) {
+        const size_t need = rows * pieces * (HD + 2) * sizeof(float);
+        PieceScratch& sc = g_piece_scratch[a.device < 64 ? a.device : 0];
+        if (a.device >= 64) pieces = 1;
+        if (pieces > 1 && sc.bytes < need) {
+            cudaStreamCaptureStatus cap = cudaStreamCaptureStatusNone;
+            cudaStreamIsCapturing(a.stream, &cap);
+            if (cap != cudaStreamCaptureStatusNone) {
+                pieces = 1;  // no allocation while a graph is being recorded: run whole units
+            } else {
+                if (sc.ptr) {
+                    cudaDeviceSynchronize();  // an earlier launch may still read the old block
+                    cudaFree(sc.ptr);
+                    sc = PieceScratch{};
+                }
+                if (cudaMalloc(&sc.ptr, need) == cudaSuccess) {
+                    sc.bytes = need;
+                } else {
+                    (void)cudaGetLastError();
+                    sc = PieceScratch{};
+                    pieces = 1;  // not enough memory for partials: run whole units
+                }
+            }
+        }
+        if (pieces > 1) {
+            part_acc = sc.ptr;
+            part_ml = sc.ptr + rows * pieces * HD;
+        }
+    }
+    FlashParams prm{(const uint32_t*)step.ptr, (float*)out.ptr, part_acc, part_ml, a.status, m_tokens, n_kv, window, ring, scale};
+    const dim3 grid(q_tiles, n_kv, pieces);
     flash_prefill_kernel<TWO_SRC><<<grid, FLASH_THREADS, smem, a.stream>>>(tq, tk0, tv0, tk1, tv1, prm);
     ++*a.launches;
-    return check_cuda(a, cudaGetLastError(), "attn_prefill_flash");
+    if (int r = check_cuda(a, cudaGetLastError(), "attn_prefill_flash")) return r;
+    if (pieces > 1) {
+        combine_pieces_kernel<<<(unsigned)((rows + 7) / 8), 256, 0, a.stream>>>(part_acc, part_ml, (float*)out.ptr, (uint32_t)rows,
+                                                                              (uint32_t)pieces);
+        ++*a.launches;
+        return check_cuda(a, cudaGetLastError(), "attn_prefill_flash combine");
+    }
+    return 0;
 }
 
 }  // namespace

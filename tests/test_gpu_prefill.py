@@ -136,6 +136,21 @@ def test_flash_is_bit_deterministic(ctx):
     assert np.array_equal(a.view(np.uint32), b.view(np.uint32))
 
 
+@pytest.mark.parametrize("pieces,m,q0,window", [(2, 100, 37, 0), (3, 200, 1531, 1024), (5, 64, 3000, 0), (16, 130, 200, 0),
+                                                (4, 1, 5, 0)])
+def test_flash_key_range_cut_into_pieces(ctx, monkeypatch, pieces, m, q0, window):
+    """Long units are cut into pieces along the keys to fill the last wave of CTAs; forced here on
+    small ragged cases, including pieces that get no tile at all and rows whose band misses a piece."""
+    q16, k16, v16, bufs = _linear_case(ctx, 0x5621 + m + q0, m, q0)
+    want = O.attention_f64(q16.astype(np.float32), k16.astype(np.float32), v16.astype(np.float32), m, q0, H, KV, D, SCALE,
+                           window=window)
+    monkeypatch.setenv("SGB_FLASH_PIECES", str(pieces))
+    got = _run_linear(ctx, "attn_prefill_flash_f16_d128", bufs, m, q0, KV, (SCALE, window))
+    assert_close(got, want, what=f"flash in {pieces} pieces m={m} q0={q0} window={window}")
+    again = _run_linear(ctx, "attn_prefill_flash_f16_d128", bufs, m, q0, KV, (SCALE, window))
+    assert np.array_equal(got.view(np.uint32), again.view(np.uint32))
+
+
 # ---- head_dim 128: ring history + chunk ------------------------------------------------------------------
 @pytest.mark.parametrize("q0,m", [(0, 64), (100, 64), (1000, 64), (1531, 64), (1531, 200), (66000, 4)])
 def test_sliding_ring_d128(ctx, q0, m):
