@@ -7,22 +7,19 @@
 // entry dequantises to f16(scale*q) first (the value attn_prefill_global_flash_sp_q8.wgsl:104
 // builds), then runs the same kernel.  Output is f32.
 //
-// One CTA per SM = 128 query tokens x the 2 query heads of one kv head: two Q tiles of 128 rows (one per
-// head) that share every K/V tile (GQA grouping), so a tile of 128 keys is loaded once for 256 rows.
-//   TMA (128B swizzle, CTA-local) -> a ring of five 32 KB slots, K(0) V(0) K(1) V(1) ...     loader warp
-//   S_h[128x128] = Q_h K^T    tcgen05.mma kind::f16, D in tensor memory                     MMA warp
-//   row softmax in registers: two threads per row of S_h, 64 keys each (tcgen05.ld 32x32b), base-2 exponent,
-//       half of the exponentials by polynomial on the FMA pipe, running max raised only when it grows by
-//       > 2^8; masks only at the band edges, tiles wholly outside [qpos+1-window, qpos] are never visited
-//                                                                        2 heads x 2 softmax warpgroups
-//   P_h -> back into tensor memory over S_h as packed f16 pairs (tcgen05.st)
-//   O_h[128x128] += P_h V     tcgen05.mma with A = P_h from tensor memory, V as the MN-major B operand
-//                             straight from its [key][dim] tile
-// The tensor pipe runs  QK0(j) PV1(j-1) QK1(j) PV0(j) QK0(j+1) ...: while the warps of head h turn S_h into P_h
-// the pipe works on the other head.  A tcgen05.mma holds its issuing thread until the pipe takes it, so the
-// softmax of a head has to fit into one QK and one PV of the other head (about 1100 cycles) or the pipe
-// idles: hence two threads per row.  All 512 tensor-memory columns are used (S0 S1 O0 O1).  Every mbarrier
-// wait is bounded; tensor memory is always freed.
+// One CTA = 64 query tokens x the 2 query heads of one kv head = 128 rows of S and O, so both
+// heads share every K/V tile (GQA grouping).  Per 64-key tile:
+//   TMA (128B swizzle, CTA-local) -> smem K, V                 loader warp
+//   S[128x64]  = Q K^T   tcgen05.mma kind::f16, D in TMEM      MMA warp, 8 instructions (K = 16 each)
+//   row softmax in registers: thread r owns TMEM lane r (tcgen05.ld 32x32b), base-2 exponent,
+//       running max raised only when it grows by > 2^8; masked tiles only at the band edges,
+//       tiles wholly outside [qpos+1-window, qpos] are never visited           4 softmax warps
+//   P -> back into tensor memory over S as packed f16 pairs (tcgen05.st)
+//   O[128x128] += P V    tcgen05.mma with A = P from tensor memory, V as the MN-major B operand straight
+//                        from its [key][dim] tile
+// S is double-buffered in TMEM and the three roles talk through mbarriers only, so Q K^T of the
+// next tile and P V of the previous one run while the softmax warps work.  Two CTAs fit per SM
+// (112 KB smem, 256 TMEM columns each).  Every mbarrier wait is bounded; TMEM is always freed.
 #include <cmath>
 #include <cstdlib>
 
@@ -38,38 +35,43 @@ namespace {
 
 constexpr int HD = 128;
 constexpr int G = 2;
-constexpr int BLOCK_TOK = 128;  // query tokens per CTA (= rows of each of the two Q tiles)
-constexpr int BLOCK_N = 128;    // keys per tile
-constexpr int WG_THREADS = 128;
-constexpr int MMA_WARP = 16, LOAD_WARP = 17;
-constexpr int FLASH_THREADS = 576;  // two softmax warpgroups per head, an MMA warp, a loader warp; 96 registers each
-constexpr int POLY_MASK = 1;        // pairs j with (j & POLY_MASK) == POLY_MASK take the polynomial exponential
-constexpr int RING = 5;                              // K/V slots
-constexpr int L2_AHEAD = 6;                          // ring items (half tile steps) between the L2 prefetch and the load
-constexpr uint32_t HALF_TILE = 128 * 128;            // one [128 rows][128 B] box = one 64-dim half of a tile
-constexpr uint32_t TILE_BYTES = 2 * HALF_TILE;       // 128 rows x 128 dims f16
-constexpr uint32_t TMEM_COLS = 512;
-constexpr uint32_t TMEM_S = 0;     // S_h at h * 128 (f32 columns); P_h of keys [64c, 64c + 64) overwrites columns [64c, 64c + 32)
-constexpr uint32_t TMEM_O = 256;   // O_h at 256 + h * 128
+constexpr int BLOCK_TOK = 64;   // query tokens per CTA
+constexpr int BLOCK_M = 128;    // rows = tokens x G
+constexpr int BLOCK_N = 64;     // keys per tile
+constexpr int SOFTMAX_THREADS = 128;
+constexpr int MMA_WARP = 4, LOAD_WARP = 5;
+constexpr int FLASH_THREADS = 192;
+constexpr int KV_STAGES = 2;
+constexpr uint32_t HALF_TILE = 64 * 128;           // one [64 rows][128 B] box
+constexpr uint32_t Q_BYTES = 2 * 2 * HALF_TILE;    // 2 dim-halves x 128 rows
+constexpr uint32_t KV_TILE_BYTES = 2 * HALF_TILE;  // 2 dim-halves x 64 keys
+constexpr uint32_t TMEM_COLS = 256;
+constexpr uint32_t TMEM_S = 0;     // S: two buffers of 64 f32 columns
+constexpr uint32_t TMEM_O = 128;   // O: 128 f32 columns
 constexpr float RESCALE_T = 8.0f;
 
-// 224 KB of tiles + 2 KB of exchange + 160 B of barriers, one CTA per SM.  Not padded to the tiles' 1024-byte alignment: the
-// dynamic shared-memory base is declared 1024-aligned instead (and checked at run time).
+// 112 KB of tiles + 128 B of barriers.  Two CTAs must fit in the SM's 228 KB next to the 1 KB the
+// system reserves per CTA, so the struct is NOT padded to its 1024-byte tile alignment: the dynamic
+// shared-memory base is declared 1024-aligned instead (and checked at run time).
 struct FlashSmem {
-    uint8_t q[G][2][HALF_TILE];   // [head][dim half][128 tokens x 128 B]
-    uint8_t kv[RING][2][HALF_TILE];  // [slot][dim half][128 keys x 128 B]
-    float xchg[G][2][WG_THREADS];  // row maximum (and at the end row sum) passed between the two threads of a row
-    uint64_t full[RING];          // TMA -> MMA warp
-    uint64_t empty[RING];         // MMA commit: the slot's tile has been consumed by both heads
-    uint64_t s_ready[G];          // MMA commit: S_h holds Q_h K^T of a tile (and O_h += P_h V of the tile before it is done)
-    uint64_t p_ready[G][2];       // the 128 threads of warpgroup c of head h: keys [64c, 64c + 64) of P_h are in tensor memory
-    uint64_t o_done[G];           // MMA commit after the last P_h V
+    uint8_t q[2][2 * HALF_TILE];             // [dim half][128 rows x 128 B]
+    uint8_t k[KV_STAGES][2][HALF_TILE];      // [stage][dim half][64 keys x 128 B]
+    uint8_t v[KV_STAGES][2][HALF_TILE];
+    uint8_t p[2 * HALF_TILE];                // [128 rows x 128 B] = 64 f16 keys per row
+    uint64_t full_k[KV_STAGES];              // TMA -> MMA warp
+    uint64_t full_v[KV_STAGES];
+    uint64_t s_ready[2];                     // MMA commit: S[b] holds Q K^T of a tile
     uint64_t q_bar;
+    // p_ready and pv_done are indexed by tile parity like S: a producer can then never be two phases
+    // ahead of a consumer that has not polled yet, whatever the relative speed of the roles.
+    uint64_t p_ready[2];                     // 128 softmax threads: P(j) is in tensor memory
+    uint64_t pv_done[2];                     // MMA commit: O += P V of a tile has completed
     uint32_t tmem_base;
-    uint32_t abort;               // a bounded wait ran out somewhere in the CTA
+    uint32_t abort;                          // a bounded wait ran out somewhere in the CTA
+    uint32_t pad[8];
 };
-static_assert(sizeof(FlashSmem) == (G + RING) * TILE_BYTES + 2048 + 160, "tiles + exchange + barriers, no padding");
-static_assert(sizeof(FlashSmem) <= 227 * 1024, "fits the per-CTA shared memory limit");
+static_assert(sizeof(FlashSmem) == 7 * 2 * HALF_TILE + 128, "tiles + barriers, no padding");
+static_assert(2 * (sizeof(FlashSmem) + 1024) <= 228 * 1024, "two CTAs per SM");
 
 struct FlashParams {
     const uint32_t* step;
@@ -84,7 +86,7 @@ struct FlashParams {
     float scale;
 };
 
-// One 128-key tile: where it comes from and which absolute positions its rows hold.
+// One 64-key tile: where it comes from and which absolute positions its rows hold.
 struct Tile {
     int src;        // 0 = history / linear, 1 = chunk
     int row0;       // TMA row coordinate of key 0 of the tile
@@ -92,10 +94,13 @@ struct Tile {
     int64_t lo, hi; // positions of this source that are real: [lo, hi]
 };
 
-// Roles: warps 0-7 = softmax of head 0, warps 8-15 = softmax of head 1 (two threads per row), warp 16 = MMA
-// issue (one thread), warp 17 = TMA loads (one thread).
+// Roles: warps 0-3 = softmax (thread r owns row r of S and O), warp 4 = MMA issue (one thread),
+// warp 5 = TMA loads (one thread).  Per tile j the tensor pipe runs, in order, ... PV(j-1) QK(j+1)
+// PV(j) QK(j+2) ...: S is double-buffered in TMEM, so QK(j+1) and PV(j-1) execute while the softmax
+// warps work on tile j, and the softmax is the only thing on the critical path of a CTA; the second
+// CTA on the SM fills the tensor pipe's remaining gaps.
 template <bool TWO_SRC>
-__global__ void __launch_bounds__(FLASH_THREADS, 1) flash_prefill_kernel(const __grid_constant__ CUtensorMap tm_q,
+__global__ void __launch_bounds__(FLASH_THREADS, 2) flash_prefill_kernel(const __grid_constant__ CUtensorMap tm_q,
                                                                          const __grid_constant__ CUtensorMap tm_k0,
                                                                          const __grid_constant__ CUtensorMap tm_v0,
                                                                          const __grid_constant__ CUtensorMap tm_k1,
@@ -164,15 +169,12 @@ __global__ void __launch_bounds__(FLASH_THREADS, 1) flash_prefill_kernel(const _
 
     // ---- set-up -----------------------------------------------------------------------------------------
     if (tid == 0) {
-        for (int i = 0; i < RING; i++) {
-            mbar_init(&sm.full[i], 1);
-            mbar_init(&sm.empty[i], 1);
-        }
-        for (int h = 0; h < G; h++) {
-            mbar_init(&sm.s_ready[h], 1);
-            mbar_init(&sm.p_ready[h][0], WG_THREADS);
-            mbar_init(&sm.p_ready[h][1], WG_THREADS);
-            mbar_init(&sm.o_done[h], 1);
+        for (int i = 0; i < KV_STAGES; i++) {
+            mbar_init(&sm.full_k[i], 1);
+            mbar_init(&sm.full_v[i], 1);
+            mbar_init(&sm.s_ready[i], 1);
+            mbar_init(&sm.p_ready[i], SOFTMAX_THREADS);
+            mbar_init(&sm.pv_done[i], 1);
         }
         mbar_init(&sm.q_bar, 1);
         sm.abort = 0;
@@ -188,161 +190,135 @@ __global__ void __launch_bounds__(FLASH_THREADS, 1) flash_prefill_kernel(const _
     const uint32_t tmem = sm.tmem_base;
     bool failed = false;
 
-    if (warp >= MMA_WARP) {
-      if (warp == LOAD_WARP) {
-        // ======================= TMA loads: ring item i = K(i/2) for even i, V(i/2) for odd i =======================
+    if (warp == LOAD_WARP) {
+        // ======================= TMA loads =======================
         if ((tid & 31) == 0) {
             tma_prefetch_desc(&tm_q);
             tma_prefetch_desc(&tm_k0);
             tma_prefetch_desc(&tm_v0);
-            mbar_arrive_expect_tx(&sm.q_bar, G * TILE_BYTES);
-            for (int h = 0; h < G; h++) {
-                tma_load_3d(sm.q[h][0], &tm_q, &sm.q_bar, 0, kvh * G + h, (int)m0);
-                tma_load_3d(sm.q[h][1], &tm_q, &sm.q_bar, 64, kvh * G + h, (int)m0);
-            }
-            for (int i = 0; i < 2 * n_tiles; ++i) {
-                const int slot = i % RING;
-                if (i >= RING) {
-                    mbar_wait(&sm.empty[slot], (i / RING - 1) & 1, prm.status, 411, failed, 100);
-                    if (failed) break;  // never write into a slot that may still be read
-                }
-                auto map_of = [&](int item, const Tile& tl) {
-                    return (item & 1) ? ((TWO_SRC && tl.src) ? &tm_v1 : &tm_v0) : ((TWO_SRC && tl.src) ? &tm_k1 : &tm_k0);
-                };
-                if (i + L2_AHEAD < 2 * n_tiles) {  // bring a tile of a later ring round into L2 now
-                    const Tile ta = tile_at((i + L2_AHEAD) >> 1);
-                    tma_prefetch_l2_3d(map_of(i + L2_AHEAD, ta), 0, kvh, ta.row0);
-                    tma_prefetch_l2_3d(map_of(i + L2_AHEAD, ta), 64, kvh, ta.row0);
-                }
-                const Tile t = tile_at(i >> 1);
-                const CUtensorMap* map = map_of(i, t);
-                mbar_arrive_expect_tx(&sm.full[slot], TILE_BYTES);
-                tma_load_3d(sm.kv[slot][0], map, &sm.full[slot], 0, kvh, t.row0);
-                tma_load_3d(sm.kv[slot][1], map, &sm.full[slot], 64, kvh, t.row0);
+            auto load_k = [&](int it) {
+                const Tile t = tile_at(it);
+                const int st = it % KV_STAGES;
+                const CUtensorMap* mk = (TWO_SRC && t.src) ? &tm_k1 : &tm_k0;
+                mbar_arrive_expect_tx(&sm.full_k[st], KV_TILE_BYTES);
+                tma_load_3d(sm.k[st][0], mk, &sm.full_k[st], 0, kvh, t.row0);
+                tma_load_3d(sm.k[st][1], mk, &sm.full_k[st], 64, kvh, t.row0);
+            };
+            auto load_v = [&](int it) {
+                const Tile t = tile_at(it);
+                const int st = it % KV_STAGES;
+                const CUtensorMap* mv = (TWO_SRC && t.src) ? &tm_v1 : &tm_v0;
+                mbar_arrive_expect_tx(&sm.full_v[st], KV_TILE_BYTES);
+                tma_load_3d(sm.v[st][0], mv, &sm.full_v[st], 0, kvh, t.row0);
+                tma_load_3d(sm.v[st][1], mv, &sm.full_v[st], 64, kvh, t.row0);
+            };
+            mbar_arrive_expect_tx(&sm.q_bar, Q_BYTES);
+            tma_load_3d(sm.q[0], &tm_q, &sm.q_bar, 0, kvh * G, (int)m0);
+            tma_load_3d(sm.q[1], &tm_q, &sm.q_bar, 64, kvh * G, (int)m0);
+            if (n_tiles > 0) load_k(0);
+            if (n_tiles > 1) load_k(1);
+            if (n_tiles > 0) load_v(0);
+            if (n_tiles > 1) load_v(1);
+            for (int j = 0; j + 2 < n_tiles; ++j) {
+                const int b = j % KV_STAGES;
+                // K stage b is free once QK(j) has completed, V stage b once PV(j) has.
+                mbar_wait(&sm.s_ready[b], (j / 2) & 1, prm.status, 411, failed, 100);
+                if (failed) break;  // never write into a stage that may still be read
+                load_k(j + 2);
+                mbar_wait(&sm.pv_done[b], (j / 2) & 1, prm.status, 412, failed, 100);
+                if (failed) break;
+                load_v(j + 2);
             }
         }
-      } else if (warp == MMA_WARP) {
+    } else if (warp == MMA_WARP) {
         // ======================= MMA issue =======================
-        // One thread issues for both heads in the order QK0(j) PV1(j-1) QK1(j) PV0(j): the softmax of a head
-        // then has one QK and one PV of the other head to finish in before the pipe would wait for it.
         if ((tid & 31) == 0) {
-            constexpr uint32_t IDESC_QK = umma_idesc_f16(128, BLOCK_N, 0, 0);
-            constexpr uint32_t IDESC_PV = umma_idesc_f16(128, HD, 0, 1);
-            // S_h = Q_h K^T: 8 MMAs of K = 16 over the two 64-dim halves
-            auto issue_qk = [&](int h, int slot) {
+            constexpr uint32_t IDESC_QK = umma_idesc_f16(BLOCK_M, BLOCK_N, 0, 0);
+            constexpr uint32_t IDESC_PV = umma_idesc_f16(BLOCK_M, HD, 0, 1);
+            // S[j % 2] = Q K(j)^T: 8 MMAs of K = 16, once K(j) has landed.
+            auto issue_qk = [&](int j) {
+                const int b = j % KV_STAGES;
+                mbar_wait(&sm.full_k[b], (j / KV_STAGES) & 1, prm.status, 402, failed);
+                if (failed) return;
+                tc_fence_after_sync();
 #pragma unroll
-                for (int half = 0; half < 2; half++) {
+                for (int h = 0; h < 2; h++) {
 #pragma unroll
                     for (int kk = 0; kk < 4; kk++) {
-                        const uint64_t da = umma_desc_sw128(smem_u32(sm.q[h][half]) + kk * 32, 16, 1024);
-                        const uint64_t db = umma_desc_sw128(smem_u32(sm.kv[slot][half]) + kk * 32, 16, 1024);
-                        umma_f16_ss(tmem + TMEM_S + h * 128, da, db, IDESC_QK, (half | kk) ? 1u : 0u);
+                        const uint64_t da = umma_desc_sw128(smem_u32(sm.q[h]) + kk * 32, 16, 1024);
+                        const uint64_t db = umma_desc_sw128(smem_u32(sm.k[b][h]) + kk * 32, 16, 1024);
+                        umma_f16_ss(tmem + TMEM_S + b * BLOCK_N, da, db, IDESC_QK, (h | kk) ? 1u : 0u);
                     }
                 }
-                umma_commit(&sm.s_ready[h]);
-            };
-            // O_h += P_h V of tile jj: 8 MMAs of K = 16 keys.  The two halves of P_h (keys 0..63, 64..127) come from
-            // different warpgroups, each as f16 pairs over the first 32 columns of the scores it was made from, and
-            // are waited for separately.
-            auto issue_pv = [&](int h, int slot, int jj, bool need_v) {
-#pragma unroll
-                for (int c = 0; c < 2; c++) {
-                    mbar_wait(&sm.p_ready[h][c], jj & 1, prm.status, 403 + c, failed);
-                    if (c == 0 && need_v) mbar_wait(&sm.full[slot], ((2 * jj + 1) / RING) & 1, prm.status, 405, failed);
-                    if (failed) return;
-                    tc_fence_after_sync();
-#pragma unroll
-                    for (int kk = 4 * c; kk < 4 * c + 4; kk++) {
-                        const uint64_t db = umma_desc_sw128(smem_u32(sm.kv[slot][0]) + kk * 2048, HALF_TILE, 1024);
-                        umma_f16_ts(tmem + TMEM_O + h * 128, tmem + TMEM_S + h * 128 + 64 * c + (kk - 4 * c) * 8, db, IDESC_PV, (jj == 0 && kk == 0) ? 0u : 1u);
-                    }
-                }
+                umma_commit(&sm.s_ready[b]);
             };
             mbar_wait(&sm.q_bar, 0, prm.status, 401, failed);
-            for (int j = 0; j < n_tiles && !failed; ++j) {
-                const int ik = 2 * j, iv = 2 * j + 1;
-                const int slot_k = ik % RING, slot_v = iv % RING;
-                mbar_wait(&sm.full[slot_k], (ik / RING) & 1, prm.status, 402, failed);
+            if (n_tiles > 0) issue_qk(0);
+            if (n_tiles > 1) issue_qk(1);
+            for (int j = 0; j < n_tiles; ++j) {
+                const int b = j % KV_STAGES;
+                mbar_wait(&sm.p_ready[b], (j / 2) & 1, prm.status, 403, failed);
+                mbar_wait(&sm.full_v[b], (j / KV_STAGES) & 1, prm.status, 405, failed);
                 if (failed) break;
                 tc_fence_after_sync();
-                issue_qk(0, slot_k);
-                if (j > 0) {
-                    issue_pv(1, (iv - 2) % RING, j - 1, false);  // V(j - 1) was waited for at P0 V(j - 1)
-                    if (failed) break;
-                    umma_commit(&sm.empty[(iv - 2) % RING]);
+#pragma unroll
+                for (int kk = 0; kk < 4; kk++) {
+                    // P(j) lives in the first 32 columns of S[b] (packed f16 pairs), written by the softmax warps
+                    const uint64_t db = umma_desc_sw128(smem_u32(sm.v[b][0]) + kk * 2048, HALF_TILE, 1024);
+                    umma_f16_ts(tmem + TMEM_O, tmem + TMEM_S + b * BLOCK_N + kk * 8, db, IDESC_PV, (j | kk) ? 1u : 0u);
                 }
-                issue_qk(1, slot_k);
-                umma_commit(&sm.empty[slot_k]);
-                issue_pv(0, slot_v, j, true);
-                if (failed) break;
-                if (j == n_tiles - 1) {
-                    umma_commit(&sm.o_done[0]);
-                    issue_pv(1, slot_v, j, false);
-                    if (failed) break;
-                    umma_commit(&sm.o_done[1]);
+                umma_commit(&sm.pv_done[b]);
+                if (j + 2 < n_tiles) {
+                    // S[b] may be overwritten: the softmax warps read it before they produced P(j), waited for above
+                    issue_qk(j + 2);
                 }
             }
         }
-      }
     } else {
-        // ======================= softmax =======================
-        // Head h = warp / 8.  Row r of its tile is shared by two threads, r of warpgroup c = 0 and of c = 1
-        // ((warp / 4) % 2), which take keys [64c, 64c + 64) of every tile and columns [64c, 64c + 64) of O: half
-        // the exponentials per thread, twice the warps to hide their latency.  The row maximum is exchanged
-        // through shared memory once per tile, so both threads carry the same running max and their sums add.
-        const int h = warp >> 3, c = (warp >> 2) & 1;
-        const int r = tid & (WG_THREADS - 1);
-        const uint32_t tok = m0 + (uint32_t)r;
+        // ======================= softmax: row r of the tile <-> TMEM lane r <-> thread r =======================
+        // token m0 + r/2, query head kvh*2 + r%2
+        const int r = tid;
+        const uint32_t tok = m0 + (uint32_t)(r >> 1);
         const int64_t qpos = q0 + tok;
         const int64_t row_lo = (prm.window != 0 && qpos + 1 > (int64_t)prm.window) ? qpos + 1 - prm.window : 0;
         const float scale2 = prm.scale * 1.4426950408889634f;  // > 0 (checked on the host)
-        const uint32_t lane_addr = tmem + ((uint32_t)((warp & 3) * 32) << 16);
-        const uint32_t s_addr = lane_addr + TMEM_S + h * 128 + c * 64;  // this thread's 64 scores; P goes over the first 32 columns
-        const uint32_t o_addr = lane_addr + TMEM_O + h * 128 + c * 64;
-        float* const my_x = &sm.xchg[h][c][r];
-        const float* const other_x = &sm.xchg[h][c ^ 1][r];
+        const uint32_t lane_addr = tmem + ((uint32_t)(warp * 32) << 16);
         float m_run = NEG_SENTINEL, l_run = 0.0f;
 
         for (int it = 0; it < n_tiles; ++it) {
+            const int b = it % 2;
             const Tile t = tile_at(it);
-            // A tile needs per-element masks only where it crosses a band edge or a source boundary.
-            const bool tile_masked = t.pos0 + BLOCK_N - 1 > first_qpos || t.pos0 < last_lo || t.pos0 < t.lo || t.pos0 + BLOCK_N - 1 > t.hi;
-            const int64_t vis_hi = min(qpos, t.hi), vis_lo = max(row_lo, t.lo);
-            auto mask32 = [&](uint32_t (&a)[32], int col0) {  // scores of keys t.pos0 + col0 .. + 31
-                if (tile_masked) {
-#pragma unroll
-                    for (int j = 0; j < 32; j++) {
-                        const int64_t pos = t.pos0 + col0 + j;
-                        if (pos < vis_lo || pos > vis_hi) a[j] = 0xff800000u;  // -inf
-                    }
-                }
-            };
-            mbar_wait(&sm.s_ready[h], it & 1, prm.status, 407, failed);
+            mbar_wait(&sm.s_ready[b], (it / 2) & 1, prm.status, 404, failed);
             tc_fence_after_sync();
-            // ---- pass 1: the row maximum of this thread's 64 raw scores (scale2 > 0 commutes with max), on four
-            // independent chains of three-input max; then the other half's through shared memory.  The scores are
-            // read again in pass 2 rather than kept: 64 live values per thread would not fit the register file.
-            float mx_half;
+            float v[64];
             {
                 uint32_t a0[32], a1[32];
-                tmem_ld_32x32b_x32(s_addr, a0);
-                tmem_ld_32x32b_x32(s_addr + 32, a1);
+                tmem_ld_32x32b_x32(lane_addr + TMEM_S + b * BLOCK_N, a0);
+                tmem_ld_32x32b_x32(lane_addr + TMEM_S + b * BLOCK_N + 32, a1);
                 tc_wait_ld();
-                mask32(a0, 64 * c);
-                mask32(a1, 64 * c + 32);
-                float mx4[4] = {__uint_as_float(a0[0]), __uint_as_float(a0[1]), __uint_as_float(a1[0]), __uint_as_float(a1[1])};
 #pragma unroll
-                for (int j = 2; j < 32; j += 2) {
-                    mx4[(j >> 1) & 1] = max3(mx4[(j >> 1) & 1], __uint_as_float(a0[j]), __uint_as_float(a0[j + 1]));
-                    mx4[2 + ((j >> 1) & 1)] = max3(mx4[2 + ((j >> 1) & 1)], __uint_as_float(a1[j]), __uint_as_float(a1[j + 1]));
+                for (int j = 0; j < 32; j++) {
+                    v[j] = __uint_as_float(a0[j]);
+                    v[32 + j] = __uint_as_float(a1[j]);
                 }
-                mx_half = fmaxf(fmaxf(mx4[0], mx4[1]), fmaxf(mx4[2], mx4[3]));
             }
-            // (One buffer is enough: the partner reads it right after the barrier, and this thread writes it
-            // again only after S of the next tile, which needs the partner's P of this one.)
-            *my_x = mx_half;
-            named_barrier_sync(1 + h, 2 * WG_THREADS);
-            const float mx = fmaxf(mx_half, *other_x) * scale2;
+
+            // A tile needs per-element masks only where it crosses a band edge or a source boundary.
+            const bool tile_masked = t.pos0 + BLOCK_N - 1 > first_qpos || t.pos0 < last_lo || t.pos0 < t.lo || t.pos0 + BLOCK_N - 1 > t.hi;
+            if (tile_masked) {
+                const int64_t hi = min(qpos, t.hi), lo = max(row_lo, t.lo);
+#pragma unroll
+                for (int j = 0; j < 64; j++) {
+                    const int64_t pos = t.pos0 + j;
+                    if (pos < lo || pos > hi) v[j] = -INFINITY;
+                }
+            }
+            // row max of the raw scores on four independent chains of three-input max; scale2 > 0
+            // commutes with max
+            float mx4[4] = {v[0], v[1], v[2], v[3]};
+#pragma unroll
+            for (int j = 4; j < 64; j += 2) mx4[(j >> 1) & 3] = max3(mx4[(j >> 1) & 3], v[j], v[j + 1]);
+            const float mx = fmaxf(fmaxf(mx4[0], mx4[1]), fmaxf(mx4[2], mx4[3])) * scale2;
             const bool grow = mx > m_run + RESCALE_T;
             float corr = 1.0f;
             if (grow) {
@@ -350,68 +326,65 @@ __global__ void __launch_bounds__(FLASH_THREADS, 1) flash_prefill_kernel(const _
                 m_run = mx;
                 l_run *= corr;
             }
-            // This thread's half of O_h is rescaled where a row's max moved (rare after the first tiles).  No
-            // wait is needed: S_h of this tile was committed after P_h V of the previous tile was issued.
-            if (it > 0 && __any_sync(0xffffffffu, grow)) {
-#pragma unroll
-                for (int cc = 0; cc < 2; cc++) {
-                    uint32_t o[32];
-                    tmem_ld_32x32b_x32(o_addr + 32 * cc, o);
-                    tc_wait_ld();
-#pragma unroll
-                    for (int j = 0; j < 32; j++) o[j] = __float_as_uint(__uint_as_float(o[j]) * corr);
-                    tmem_st_32x32b_x32(o_addr + 32 * cc, o);
-                }
-            }
-            // ---- pass 2: p = 2^(s * scale2 - m), 32 keys at a time, with the multiply-add and the running sums
-            // on packed f32x2 pipes.  The 16 columns of P overwrite scores this thread has already read.
+            // p = 2^(s * scale2 - m) with the multiply-add and the running sums on packed f32x2 pipes
             const float2 sc2 = make_float2(scale2, scale2), neg_m = make_float2(-m_run, -m_run);
+            uint32_t pk[32];
             float2 ls4[4] = {make_float2(0.0f, 0.0f), make_float2(0.0f, 0.0f), make_float2(0.0f, 0.0f), make_float2(0.0f, 0.0f)};
 #pragma unroll
-            for (int cc = 0; cc < 2; cc++) {
-                uint32_t a[32], pk[16];
-                tmem_ld_32x32b_x32(s_addr + 32 * cc, a);
-                tc_wait_ld();
-                mask32(a, 64 * c + 32 * cc);
-#pragma unroll
-                for (int j = 0; j < 16; j++) {
-                    const float2 x = __ffma2_rn(make_float2(__uint_as_float(a[2 * j]), __uint_as_float(a[2 * j + 1])), sc2, neg_m);
-                    // some pairs take the polynomial on the FMA pipe: the special-function unit does 16
-                    // exponentials per clock and SM, which is exactly what the tensor pipe can consume
-                    const float2 pp = ((j & POLY_MASK) == POLY_MASK) ? ex2_poly2(x) : make_float2(ex2(x.x), ex2(x.y));
-                    ls4[j & 3] = __fadd2_rn(ls4[j & 3], pp);  // l in f32 from the unrounded p (attn_prefill_global_flash_sp.wgsl:147-156)
-                    pk[j] = pack_half2(pp.x, pp.y);
-                }
-                tmem_st_32x32b_x16(s_addr + 16 * cc, pk);
+            for (int j = 0; j < 32; j++) {
+                const float2 x = __ffma2_rn(make_float2(v[2 * j], v[2 * j + 1]), sc2, neg_m);
+                const float2 pp = make_float2(ex2(x.x), ex2(x.y));
+                ls4[j & 3] = __fadd2_rn(ls4[j & 3], pp);  // l in f32 from the unrounded p (attn_prefill_global_flash_sp.wgsl:147-156)
+                pk[j] = pack_half2(pp.x, pp.y);
             }
             l_run += ((ls4[0].x + ls4[0].y) + (ls4[1].x + ls4[1].y)) + ((ls4[2].x + ls4[2].y) + (ls4[3].x + ls4[3].y));
+
+            // O is rescaled where a row's max moved (rare after the first tiles), and only once P V of the
+            // previous tile has completed.  P(it) itself needs no such wait: it goes into S[b], which the
+            // tensor pipe next touches with P V(it).  (Most tiles skip this wait; its parity stays
+            // unambiguous because pv_done[b ^ 1] is next committed by P V(it + 1), which needs this
+            // thread's P(it + 1).)
+            if (it > 0 && __any_sync(0xffffffffu, grow)) {
+                mbar_wait(&sm.pv_done[b ^ 1], ((it - 1) / 2) & 1, prm.status, 407, failed);
+                tc_fence_after_sync();
+                {
+#pragma unroll
+                    for (int c = 0; c < 4; c++) {
+                        uint32_t o[32];
+                        tmem_ld_32x32b_x32(lane_addr + TMEM_O + 32 * c, o);
+                        tc_wait_ld();
+#pragma unroll
+                        for (int j = 0; j < 32; j++) o[j] = __float_as_uint(__uint_as_float(o[j]) * corr);
+                        tmem_st_32x32b_x32(lane_addr + TMEM_O + 32 * c, o);
+                    }
+                    tc_wait_st();
+                }
+            }
+            // P row r goes back into tensor memory over the first half of S[b] (this thread has S in
+            // registers; Q K^T of tile it + 2 overwrites the buffer only after P V of this tile, because the
+            // tensor pipe runs in order).
+            tmem_st_32x32b_x32(lane_addr + TMEM_S + b * BLOCK_N, pk);
             tc_wait_st();
             tc_fence_before_sync();
-            mbar_arrive(&sm.p_ready[h][c]);
+            mbar_arrive(&sm.p_ready[b]);
         }
-        // the row sum is the two halves' (same running max); the first barrier lets the partner finish
-        // reading the last maximum before the slot is reused
-        named_barrier_sync(1 + h, 2 * WG_THREADS);
-        *my_x = l_run;
-        named_barrier_sync(1 + h, 2 * WG_THREADS);
-        l_run += *other_x;
-        if (n_tiles > 0) mbar_wait(&sm.o_done[h], 0, prm.status, 408, failed);
+        // the tensor pipe completes in order: the last P V done means all of them are
+        if (n_tiles > 0) mbar_wait(&sm.pv_done[(n_tiles - 1) & 1], ((n_tiles - 1) / 2) & 1, prm.status, 408, failed);
         tc_fence_after_sync();
 
-        // ---- epilogue: out = O / l, or this piece's partial; this thread writes dims [64c, 64c + 64) of its
-        // row.  The TMEM loads are warp-wide, so every thread takes part and only the stores are predicated
-        // (rows past the end of the chunk are not written). ----
-        const bool live = (uint32_t)r < tok_in_tile;
-        const size_t row = (size_t)(live ? tok : m0) * (prm.n_kv * G) + kvh * G + h;
+        // ---- epilogue: out = O / l, or this piece's partial.  The TMEM loads are warp-wide, so every thread
+        // takes part and only the stores are predicated (rows past the end of the chunk are not written). ----
+        const bool live = (uint32_t)(r >> 1) < tok_in_tile;
+        const size_t row = (size_t)(live ? tok : m0) * (prm.n_kv * G) + kvh * G + (r & 1);
         const bool whole = gridDim.z == 1;
         const float mul = whole ? 1.0f / l_run : 1.0f;
-        float* orow = (whole ? prm.out + row * HD : prm.part_acc + (row * gridDim.z + blockIdx.z) * HD) + 64 * c;
-        if (!whole && live && c == 0) *reinterpret_cast<float2*>(prm.part_ml + (row * gridDim.z + blockIdx.z) * 2) = make_float2(m_run, l_run);
+        float* orow = whole ? prm.out + row * HD : prm.part_acc + (row * gridDim.z + blockIdx.z) * HD;
+        if (!whole && live) *reinterpret_cast<float2*>(prm.part_ml + (row * gridDim.z + blockIdx.z) * 2) = make_float2(m_run, l_run);
 #pragma unroll
-        for (int cc = 0; cc < 2; cc++) {
+        for (int c = 0; c < 4; c++) {
             uint32_t o[32];
             if (n_tiles > 0) {  // uniform over the CTA
-                tmem_ld_32x32b_x32(o_addr + 32 * cc, o);
+                tmem_ld_32x32b_x32(lane_addr + TMEM_O + 32 * c, o);
                 tc_wait_ld();
             } else {
 #pragma unroll
@@ -420,7 +393,7 @@ __global__ void __launch_bounds__(FLASH_THREADS, 1) flash_prefill_kernel(const _
             if (live) {
 #pragma unroll
                 for (int j = 0; j < 8; j++)
-                    *reinterpret_cast<float4*>(orow + 32 * cc + 4 * j) =
+                    *reinterpret_cast<float4*>(orow + 32 * c + 4 * j) =
                         make_float4(__uint_as_float(o[4 * j]) * mul, __uint_as_float(o[4 * j + 1]) * mul,
                                     __uint_as_float(o[4 * j + 2]) * mul, __uint_as_float(o[4 * j + 3]) * mul);
             }
@@ -540,7 +513,7 @@ int run_flash(const LaunchArgs& a, const BufView& q, const BufView& k0, const Bu
     if (step.bytes < 16) return fail_validation(a, "flash prefill: the step buffer holds 4 x u32");
     if (reinterpret_cast<uintptr_t>(out.ptr) & 15) return fail_validation(a, "flash prefill: out must be 16-byte aligned");
     CUtensorMap tq, tk0, tv0, tk1, tv1;
-    if (int r = encode_qkv_map(a, &tq, BufView{q.ptr, (size_t)m_tokens * n_q * HD * 2}, n_q, 1, BLOCK_TOK, "q")) return r;
+    if (int r = encode_qkv_map(a, &tq, BufView{q.ptr, (size_t)m_tokens * n_q * HD * 2}, n_q, G, BLOCK_TOK, "q")) return r;
     if (int r = encode_qkv_map(a, &tk0, k0, n_kv, 1, BLOCK_N, "k")) return r;
     if (int r = encode_qkv_map(a, &tv0, v0, n_kv, 1, BLOCK_N, "v")) return r;
     if (TWO_SRC) {
@@ -565,7 +538,7 @@ int run_flash(const LaunchArgs& a, const BufView& q, const BufView& k0, const Bu
     }
     const uint32_t q_tiles = (m_tokens + BLOCK_TOK - 1) / BLOCK_TOK;
     const size_t rows = (size_t)m_tokens * n_q;
-    int pieces = TWO_SRC ? 1 : choose_pieces((size_t)q_tiles * n_kv, a.sm_count, k0.bytes / ((size_t)n_kv * HD * 2));
+    int pieces = TWO_SRC ? 1 : choose_pieces((size_t)q_tiles * n_kv, 2 * a.sm_count, k0.bytes / ((size_t)n_kv * HD * 2));
     float* part_acc = nullptr;
     float* part_ml = nullptr;
     if (pieces > 1) {
