@@ -288,3 +288,37 @@ def prefill_flash_f32(q_f16, ks: KvSrc, vs: KvSrc, m, q0, n_q, n_kv, hd, window,
     lib().sgo_prefill_flash_f32(_p(q), C.byref(a), C.byref(b), _p(out), m, q0, n_q, n_kv, hd, window, scale, tile_k,
                                 _p(tok), 0 if tok is None else tok.size)
     return out
+
+
+# ---- pre-attention elementwise steps (crates/sg-gpu/tests/reference/mod.rs:156-216) -------------------------
+def rmsnorm_f64(x, w, row_len: int, eps: float = 1e-6, plus_one: bool = False) -> np.ndarray:
+    """RMSNorm over rows of `row_len` in f64, rounded to f32 (reference/mod.rs:156-172)."""
+    x64 = np.asarray(x, np.float64).reshape(-1, row_len)
+    w64 = np.asarray(w, np.float64).reshape(row_len)
+    inv = 1.0 / np.sqrt((x64 * x64).sum(axis=1, keepdims=True) / row_len + eps)
+    return (x64 * inv * ((1.0 + w64) if plus_one else w64)).astype(np.float32).reshape(-1)
+
+
+def inv_freqs(rot_dims: int, theta: float) -> np.ndarray:
+    """theta^(-2i/rot_dims), i < rot_dims/2 (reference/mod.rs:176-180)."""
+    i = np.arange(rot_dims // 2, dtype=np.float64)
+    return np.power(np.float64(theta), -2.0 * i / rot_dims)
+
+
+def cos_sin_table(inv_freq, start_pos: int, tokens: int) -> np.ndarray:
+    """[token x half_rot] of interleaved (cos, sin): f64 math, f32 storage (reference/mod.rs:185-197)."""
+    pos = (np.arange(tokens, dtype=np.float64) + float(start_pos))[:, None] * np.asarray(inv_freq, np.float64)[None, :]
+    return np.stack([np.cos(pos), np.sin(pos)], axis=-1).astype(np.float32).reshape(-1)
+
+
+def rope_f64(x, head_dim: int, rot_dims: int, n_heads: int, cos_sin) -> np.ndarray:
+    """Rotate-half (NeoX) RoPE over rows [token x head x head_dim]: pair i couples dims (i, i + head_dim/2),
+    only the first rot_dims/2 pairs rotate; f64 math, rounded to f32 (reference/mod.rs:202-216)."""
+    live, partner = rot_dims // 2, head_dim // 2
+    rows = np.asarray(x, np.float64).reshape(-1, n_heads, head_dim).copy()
+    cs = np.asarray(cos_sin, np.float32).astype(np.float64).reshape(rows.shape[0], live, 2)
+    c, s = cs[:, None, :, 0], cs[:, None, :, 1]
+    a, b = rows[:, :, :live].copy(), rows[:, :, partner:partner + live].copy()
+    rows[:, :, :live] = a * c - b * s
+    rows[:, :, partner:partner + live] = b * c + a * s
+    return rows.astype(np.float32).reshape(-1)

@@ -1,0 +1,334 @@
+// The steps between the QKV projections and the attention kernels: per-head RMS norm (QK-norm, weightless
+// V-norm), rotate-half RoPE from a host-filled cos/sin table, and the quantise-and-append of K and V.
+//
+// Reference chain per layer (crates/sg-model/src/graph.rs:552-610): rmsnorm(q), rmsnorm(k), rmsnorm(v, ones),
+// rope(q), rope(k), append(k), append(v) -- seven launches with an f16 round trip between every two.  Here:
+//   rmsnorm_256/512[_plus1], rope_sliding_q/k, rope_global_q/k   the reference's names, bindings and grids
+//       (crates/sg-gpu/shaders/rmsnorm.wgsl, rope.wgsl; build.rs:84-157)
+//   attn_norm_rope_d128                       norm + rope of a [rows x 128] tensor in one pass
+//   kv_norm_rope_append_paged_q8_d128         norm(k) + rope(k) + norm(v) + Q8_0 quantise + paged append
+// The fused kernels round to f16 exactly where the chain stores f16 (after the norm, after the rotation), so
+// they give the bits of their own unfused pieces.  All of it is HBM-bound: 64-byte accesses, one 32-value
+// block per thread, the row's sum of squares combined with a fixed shuffle tree (deterministic).
+//
+// Arithmetic (f32): inv = 1/sqrt(sum(x^2)/n + 1e-6); y = f16(x * inv * w)  [w or 1 + w];
+// rope pair i couples dims (i, i + n/2), live for i < rot_dims/2: lo' = f16(lo*c - hi*s), hi' = f16(hi*c + lo*s).
+#include "sgb_common.cuh"
+#include "sgb_kernels.h"
+
+namespace sgb {
+
+namespace {
+
+constexpr int PRE_THREADS = 256;
+constexpr float RMS_EPS = 1e-6f;
+
+__device__ __forceinline__ void load_f16x32(const __half* p, float (&x)[32])
+{
+    const uint4* v = reinterpret_cast<const uint4*>(p);
+#pragma unroll
+    for (int i = 0; i < 4; i++) {
+        const uint4 u = __ldg(v + i);
+        const __half2* h = reinterpret_cast<const __half2*>(&u);
+#pragma unroll
+        for (int j = 0; j < 4; j++) {
+            const float2 f = __half22float2(h[j]);
+            x[i * 8 + j * 2] = f.x;
+            x[i * 8 + j * 2 + 1] = f.y;
+        }
+    }
+}
+
+__device__ __forceinline__ void pack_f16x32(const float (&x)[32], uint4 (&out)[4])
+{
+#pragma unroll
+    for (int i = 0; i < 4; i++) {
+        uint32_t w[4];
+#pragma unroll
+        for (int j = 0; j < 4; j++) {
+            const __half2 h = __floats2half2_rn(x[i * 8 + j * 2], x[i * 8 + j * 2 + 1]);
+            w[j] = *reinterpret_cast<const uint32_t*>(&h);
+        }
+        out[i] = make_uint4(w[0], w[1], w[2], w[3]);
+    }
+}
+
+__device__ __forceinline__ float round_f16(float v) { return __half2float(__float2half_rn(v)); }
+
+// Sum of squares of a row spread over BPR consecutive lanes (one 32-value block each): in-thread sum in index
+// order, then an xor butterfly, which gives every lane the same bits.
+template <int BPR>
+__device__ __forceinline__ float row_inv_rms(const float (&x)[32])
+{
+    float ss = 0.0f;
+#pragma unroll
+    for (int i = 0; i < 32; i++) ss = fmaf(x[i], x[i], ss);
+#pragma unroll
+    for (int d = 1; d < BPR; d <<= 1) ss += __shfl_xor_sync(0xffffffffu, ss, d);
+    return rsqrtf(ss / (float)(BPR * 32) + RMS_EPS);
+}
+
+// y = f16(x * inv * weight) for this thread's block; PLUS_ONE: weight = 1 + w (rmsnorm.wgsl:52-58); w == nullptr: 1.
+template <bool PLUS_ONE>
+__device__ __forceinline__ void apply_norm(float (&x)[32], float inv, const float* __restrict__ w)
+{
+#pragma unroll
+    for (int i = 0; i < 32; i++) {
+        float weight = 1.0f;
+        if (w != nullptr) weight = PLUS_ONE ? 1.0f + __ldg(w + i) : __ldg(w + i);
+        x[i] = round_f16(x[i] * inv * weight);
+    }
+}
+
+// rmsnorm_<ROW_LEN>[_plus1]: x f16[rows x ROW_LEN], w f32[ROW_LEN], y f16.  grid [rows].
+template <int BPR, bool PLUS_ONE>
+__global__ void __launch_bounds__(PRE_THREADS) rmsnorm_kernel(const __half* __restrict__ x, const float* __restrict__ w,
+                                                              __half* __restrict__ y, size_t n_blocks)
+{
+    const size_t blk = (size_t)blockIdx.x * PRE_THREADS + threadIdx.x;
+    const bool live = blk < n_blocks;  // whole rows only, and BPR divides 32: a row never straddles a warp
+    float v[32];
+    if (live) {
+        load_f16x32(x + blk * 32, v);
+    } else {
+#pragma unroll
+        for (int i = 0; i < 32; i++) v[i] = 0.0f;
+    }
+    const float inv = row_inv_rms<BPR>(v);
+    if (!live) return;
+    apply_norm<PLUS_ONE>(v, inv, w + (blk % BPR) * 32);
+    uint4 out[4];
+    pack_f16x32(v, out);
+    uint4* o = reinterpret_cast<uint4*>(y + blk * 32);
+#pragma unroll
+    for (int i = 0; i < 4; i++) o[i] = out[i];
+}
+
+// rope_*: in place over rows [token x head x head_dim], one thread per (row, live pair) (rope.wgsl:36-52).
+__global__ void __launch_bounds__(PRE_THREADS) rope_kernel(__half* __restrict__ xs, const float2* __restrict__ cos_sin,
+                                                           uint32_t head_dim, uint32_t half_rot, uint32_t n_heads, size_t pairs_total)
+{
+    const size_t g = (size_t)blockIdx.x * PRE_THREADS + threadIdx.x;
+    if (g >= pairs_total) return;
+    const size_t row = g / half_rot;
+    const uint32_t pair = (uint32_t)(g % half_rot);
+    const size_t token = row / n_heads;
+    const float2 cs = __ldg(cos_sin + token * half_rot + pair);
+    __half* lo = xs + row * head_dim + pair;
+    __half* hi = lo + head_dim / 2;
+    const float a = __half2float(*lo), b = __half2float(*hi);
+    *lo = __float2half_rn(__fsub_rn(__fmul_rn(a, cs.x), __fmul_rn(b, cs.y)));
+    *hi = __float2half_rn(__fadd_rn(__fmul_rn(b, cs.x), __fmul_rn(a, cs.y)));
+}
+
+// One 32-dim block of a 128-dim row after norm and rotation, as f16-exact floats.  The four threads of a row
+// are consecutive lanes; thread `sub` owns dims [32 sub, 32 sub + 32) and reads its rotation partner's block
+// (dims +-64) again from memory, which the partner thread has just pulled into L1.
+template <bool PLUS_ONE>
+__device__ __forceinline__ void norm_rope_block_d128(const __half* __restrict__ row_ptr, const float* __restrict__ w,
+                                                      const float2* __restrict__ cs_row, uint32_t half_rot, int sub, bool live,
+                                                      float (&own)[32])
+{
+    float other[32];
+    if (live) {
+        load_f16x32(row_ptr + sub * 32, own);
+    } else {
+#pragma unroll
+        for (int i = 0; i < 32; i++) own[i] = 0.0f;
+    }
+    const float inv = row_inv_rms<4>(own);
+    if (!live) return;
+    const int psub = sub ^ 2;
+    const bool rotates = half_rot > (uint32_t)((sub & 1) * 32);  // any live pair among this block's 32
+    if (rotates) load_f16x32(row_ptr + psub * 32, other);
+    apply_norm<PLUS_ONE>(own, inv, w ? w + sub * 32 : nullptr);
+    if (!rotates) return;
+    apply_norm<PLUS_ONE>(other, inv, w ? w + psub * 32 : nullptr);
+#pragma unroll
+    for (int i = 0; i < 32; i++) {
+        const uint32_t pair = (uint32_t)((sub & 1) * 32 + i);
+        if (pair < half_rot) {
+            const float2 cs = __ldg(cs_row + pair);
+            // low half: lo*c - hi*s with lo = own; high half: hi*c + lo*s with hi = own
+            own[i] = (sub < 2) ? round_f16(__fsub_rn(__fmul_rn(own[i], cs.x), __fmul_rn(other[i], cs.y)))
+                               : round_f16(__fadd_rn(__fmul_rn(own[i], cs.x), __fmul_rn(other[i], cs.y)));
+        }
+    }
+}
+
+// attn_norm_rope_d128: x f16[rows x 128] (rows = tokens x n_heads), w f32[128], cos_sin f32[tokens x rot/2 x 2], y f16.
+template <bool PLUS_ONE>
+__global__ void __launch_bounds__(PRE_THREADS) norm_rope_d128_kernel(const __half* __restrict__ x, const float* __restrict__ w,
+                                                                     const float2* __restrict__ cos_sin, __half* __restrict__ y,
+                                                                     uint32_t n_heads, uint32_t half_rot, size_t n_blocks)
+{
+    const size_t blk = (size_t)blockIdx.x * PRE_THREADS + threadIdx.x;
+    const bool live = blk < n_blocks;
+    const size_t row = blk / 4;
+    const int sub = (int)(blk % 4);
+    float v[32];
+    norm_rope_block_d128<PLUS_ONE>(x + row * 128, w, cos_sin + (row / n_heads) * half_rot, half_rot, sub, live, v);
+    if (!live) return;
+    uint4 out[4];
+    pack_f16x32(v, out);
+    uint4* o = reinterpret_cast<uint4*>(y + blk * 32);
+#pragma unroll
+    for (int i = 0; i < 4; i++) o[i] = out[i];
+}
+
+// Q8_0 of one block of f16-exact values: the arithmetic of kv_quant_q8.wgsl:38-57 (see kv_codec.cu).
+__device__ __forceinline__ void quant_block_f32(const float (&x)[32], __half& scale, uint32_t (&packed)[8])
+{
+    float amax = 0.0f;
+#pragma unroll
+    for (int i = 0; i < 32; i++) amax = fmaxf(amax, fabsf(x[i]));
+    const float d = __fmul_rn(amax, 1.0f / 127.0f);
+    const float id = d > 0.0f ? __fdiv_rn(1.0f, d) : 0.0f;
+    scale = __float2half_rn(d);
+#pragma unroll
+    for (int w = 0; w < 8; w++) {
+        uint32_t p = 0;
+#pragma unroll
+        for (int b = 0; b < 4; b++) p |= (uint32_t)(__float2int_rn(__fmul_rn(x[w * 4 + b], id)) & 0xFF) << (8 * b);
+        packed[w] = p;
+    }
+}
+
+// kv_norm_rope_append_paged_q8_d128: blocks [0, n) are K (norm with k_w, rope), blocks [n, 2n) are V (weightless
+// norm); each lands Q8_0-quantised at row page_table[t / page] * page + t % page, t = step[0] + token.
+template <bool PLUS_ONE>
+__global__ void __launch_bounds__(PRE_THREADS)
+    kv_norm_rope_append_kernel(const __half* __restrict__ k_raw, const __half* __restrict__ v_raw, const float* __restrict__ k_w,
+                               const float2* __restrict__ cos_sin, __half* __restrict__ k_scales, int8_t* __restrict__ k_quants,
+                               __half* __restrict__ v_scales, int8_t* __restrict__ v_quants, const uint32_t* __restrict__ page_table,
+                               uint32_t table_len, uint32_t page, const uint32_t* __restrict__ step, uint32_t n_kv, uint32_t half_rot,
+                               size_t n_blocks, size_t dst_rows, uint32_t* status)
+{
+    const size_t g = (size_t)blockIdx.x * PRE_THREADS + threadIdx.x;
+    const bool live = g < 2 * n_blocks;  // n_blocks is a multiple of 4: K and V never share a row's four lanes
+    const bool is_v = g >= n_blocks;
+    const size_t blk = is_v ? g - n_blocks : g;
+    const size_t row = blk / 4;  // (token, kv head)
+    const int sub = (int)(blk % 4);
+    const size_t token = row / n_kv;
+    float v[32];
+    norm_rope_block_d128<PLUS_ONE>((is_v ? v_raw : k_raw) + row * 128, is_v ? nullptr : k_w, cos_sin + token * half_rot,
+                                   is_v ? 0u : half_rot, sub, live, v);
+    if (!live) return;
+    const size_t t = (size_t)step[STEP_POS] + token;
+    const size_t p = t / page;
+    if (p >= table_len) {
+        report_error(status, DEV_ERR_BOUNDS, 104, (uint32_t)p, table_len);
+        return;
+    }
+    const size_t dst_row = (size_t)page_table[p] * page + t % page;
+    if (dst_row >= dst_rows) {
+        report_error(status, DEV_ERR_BOUNDS, 105, (uint32_t)dst_row, (uint32_t)dst_rows);
+        return;
+    }
+    __half s;
+    uint32_t packed[8];
+    quant_block_f32(v, s, packed);
+    const size_t dblk = (dst_row * n_kv + row % n_kv) * 4 + sub;
+    (is_v ? v_scales : k_scales)[dblk] = s;
+    uint4* o = reinterpret_cast<uint4*>((is_v ? v_quants : k_quants) + dblk * 32);
+    o[0] = make_uint4(packed[0], packed[1], packed[2], packed[3]);
+    o[1] = make_uint4(packed[4], packed[5], packed[6], packed[7]);
+}
+
+inline uint32_t grid_for(size_t n) { return (uint32_t)((n + PRE_THREADS - 1) / PRE_THREADS); }
+
+struct PushNormRope {
+    uint32_t n_heads, rot_dims, plus_one;
+};
+struct PushKvNormRope {
+    uint32_t row_len, page, rot_dims, plus_one;
+};
+
+}  // namespace
+
+template <int ROW_LEN, int PLUS_ONE>
+int launch_rmsnorm(const LaunchArgs& a)
+{
+    static_assert(ROW_LEN % 32 == 0 && 32 % (ROW_LEN / 32) == 0, "a row is 1..32 blocks that divide a warp");
+    if (a.b[0].bytes % (ROW_LEN * 2)) return fail_validation(a, "rmsnorm: x is not whole rows");
+    if (int r = need_bytes(a, 1, ROW_LEN * 4, "w")) return r;
+    if (int r = need_bytes(a, 2, a.b[0].bytes, "y")) return r;
+    const size_t n_blocks = a.b[0].bytes / 64;
+    if (n_blocks == 0) return 0;
+    rmsnorm_kernel<ROW_LEN / 32, PLUS_ONE != 0><<<grid_for(n_blocks), PRE_THREADS, 0, a.stream>>>(
+        (const __half*)a.b[0].ptr, (const float*)a.b[1].ptr, (__half*)a.b[2].ptr, n_blocks);
+    ++*a.launches;
+    return check_cuda(a, cudaGetLastError(), "rmsnorm");
+}
+template int launch_rmsnorm<256, 0>(const LaunchArgs&);
+template int launch_rmsnorm<256, 1>(const LaunchArgs&);
+template int launch_rmsnorm<512, 0>(const LaunchArgs&);
+template int launch_rmsnorm<512, 1>(const LaunchArgs&);
+
+template <int HEAD_DIM, int ROT_DIMS, int N_HEADS>
+int launch_rope(const LaunchArgs& a)
+{
+    if (a.b[0].bytes % (HEAD_DIM * 2 * N_HEADS)) return fail_validation(a, "rope: xs is not whole tokens");
+    const size_t rows = a.b[0].bytes / (HEAD_DIM * 2);
+    const size_t pairs = rows * (ROT_DIMS / 2);
+    if (int r = need_bytes(a, 1, rows / N_HEADS * (ROT_DIMS / 2) * 8, "cos_sin")) return r;
+    if (pairs == 0) return 0;
+    rope_kernel<<<grid_for(pairs), PRE_THREADS, 0, a.stream>>>((__half*)a.b[0].ptr, (const float2*)a.b[1].ptr, HEAD_DIM, ROT_DIMS / 2,
+                                                                 N_HEADS, pairs);
+    ++*a.launches;
+    return check_cuda(a, cudaGetLastError(), "rope");
+}
+template int launch_rope<256, 256, 32>(const LaunchArgs&);
+template int launch_rope<256, 256, 16>(const LaunchArgs&);
+template int launch_rope<512, 128, 32>(const LaunchArgs&);
+template int launch_rope<512, 128, 4>(const LaunchArgs&);
+
+// attn_norm_rope_d128: x, w, cos_sin, y.  push {n_heads, rot_dims (0 = no rotation), plus_one}.
+int launch_norm_rope_d128(const LaunchArgs& a)
+{
+    const PushNormRope p = *(const PushNormRope*)a.push;
+    if (p.n_heads == 0 || p.rot_dims > 128 || p.rot_dims % 2) return fail_validation(a, "attn_norm_rope_d128: n_heads > 0, even rot_dims <= 128");
+    if (a.b[0].bytes % (256 * (size_t)p.n_heads)) return fail_validation(a, "attn_norm_rope_d128: x is not whole tokens of n_heads x 128");
+    const size_t rows = a.b[0].bytes / 256;
+    if (int r = need_bytes(a, 1, 128 * 4, "w")) return r;
+    if (int r = need_bytes(a, 2, rows / p.n_heads * (p.rot_dims / 2) * 8, "cos_sin")) return r;
+    if (int r = need_bytes(a, 3, a.b[0].bytes, "y")) return r;
+    const size_t n_blocks = rows * 4;
+    if (n_blocks == 0) return 0;
+    auto kern = p.plus_one ? norm_rope_d128_kernel<true> : norm_rope_d128_kernel<false>;
+    kern<<<grid_for(n_blocks), PRE_THREADS, 0, a.stream>>>((const __half*)a.b[0].ptr, (const float*)a.b[1].ptr, (const float2*)a.b[2].ptr,
+                                                          (__half*)a.b[3].ptr, p.n_heads, p.rot_dims / 2, n_blocks);
+    ++*a.launches;
+    return check_cuda(a, cudaGetLastError(), "attn_norm_rope_d128");
+}
+
+// kv_norm_rope_append_paged_q8_d128: k_raw, v_raw f16[n x row_len], k_w f32[128], cos_sin, k_scales, k_quants,
+// v_scales, v_quants, page_table, step.  push {row_len, page, rot_dims, plus_one}.
+int launch_kv_norm_rope_append_paged_q8_d128(const LaunchArgs& a)
+{
+    const PushKvNormRope p = *(const PushKvNormRope*)a.push;
+    if (p.row_len == 0 || p.row_len % 128 || p.page == 0 || p.rot_dims > 128 || p.rot_dims % 2)
+        return fail_validation(a, "kv_norm_rope_append_paged_q8_d128: row_len = n_kv_heads*128, page > 0, even rot_dims <= 128");
+    if (a.b[0].bytes % (p.row_len * 2) || a.b[1].bytes != a.b[0].bytes)
+        return fail_validation(a, "kv_norm_rope_append_paged_q8_d128: k_raw and v_raw must be the same whole rows");
+    const size_t tokens = a.b[0].bytes / (p.row_len * 2);
+    if (int r = need_bytes(a, 2, 128 * 4, "k_w")) return r;
+    if (int r = need_bytes(a, 3, tokens * (p.rot_dims / 2) * 8, "cos_sin")) return r;
+    if (int r = need_bytes(a, 9, 16, "step")) return r;
+    const size_t dst_rows = a.b[5].bytes / p.row_len;
+    if (a.b[7].bytes / p.row_len != dst_rows) return fail_validation(a, "kv_norm_rope_append_paged_q8_d128: K and V pools differ in rows");
+    if (a.b[4].bytes / 2 < dst_rows * (p.row_len / 32) || a.b[6].bytes / 2 < dst_rows * (p.row_len / 32))
+        return fail_validation(a, "kv_norm_rope_append_paged_q8_d128: scales buffer too short for the quants buffer");
+    const size_t n_blocks = a.b[0].bytes / 64;
+    if (n_blocks == 0) return 0;
+    auto kern = p.plus_one ? kv_norm_rope_append_kernel<true> : kv_norm_rope_append_kernel<false>;
+    kern<<<grid_for(2 * n_blocks), PRE_THREADS, 0, a.stream>>>(
+        (const __half*)a.b[0].ptr, (const __half*)a.b[1].ptr, (const float*)a.b[2].ptr, (const float2*)a.b[3].ptr, (__half*)a.b[4].ptr,
+        (int8_t*)a.b[5].ptr, (__half*)a.b[6].ptr, (int8_t*)a.b[7].ptr, (const uint32_t*)a.b[8].ptr, (uint32_t)(a.b[8].bytes / 4), p.page,
+        (const uint32_t*)a.b[9].ptr, p.row_len / 128, p.rot_dims / 2, n_blocks, dst_rows, a.status);
+    ++*a.launches;
+    return check_cuda(a, cudaGetLastError(), "kv_norm_rope_append_paged_q8_d128");
+}
+
+}  // namespace sgb

@@ -52,6 +52,17 @@ const KernelEntry REGISTRY[] = {
     {"kv_quant_q8", {256, 1, 1}, 3, 0, "src f16[n], scales f16[n/32], quants i8[n] | covers src.len/32 blocks", launch_kv_quant_q8},
     {"kv_dequant_q8", {256, 1, 1}, 3, 0, "scales f16[n/32], quants i8[n], dst f16[n] | covers dst.len/32 blocks", launch_kv_dequant_q8},
 
+    {"rmsnorm_256", {256, 1, 1}, 3, 0, "x f16[rows x256], w f32[256], y f16 | grid [rows]; y = x * rsqrt(mean(x^2) + 1e-6) * w", launch_rmsnorm<256, 0>},
+    {"rmsnorm_256_plus1", {256, 1, 1}, 3, 0, "as rmsnorm_256 with weight 1 + w", launch_rmsnorm<256, 1>},
+    {"rmsnorm_512", {256, 1, 1}, 3, 0, "x f16[rows x512], w f32[512], y f16 | grid [rows]", launch_rmsnorm<512, 0>},
+    {"rmsnorm_512_plus1", {256, 1, 1}, 3, 0, "as rmsnorm_512 with weight 1 + w", launch_rmsnorm<512, 1>},
+    {"rope_sliding_q", {256, 1, 1}, 2, 0, "xs f16[token x32x256] in place, cos_sin f32[token x128 x2] | grid covers rows*128 pairs; pair i = dims (i, i+128)",
+     launch_rope<256, 256, 32>},
+    {"rope_sliding_k", {256, 1, 1}, 2, 0, "xs f16[token x16x256] in place, cos_sin f32[token x128 x2]", launch_rope<256, 256, 16>},
+    {"rope_global_q", {256, 1, 1}, 2, 0, "xs f16[token x32x512] in place, cos_sin f32[token x64 x2] | pair i = dims (i, i+256), i < 64 rotate",
+     launch_rope<512, 128, 32>},
+    {"rope_global_k", {256, 1, 1}, 2, 0, "xs f16[token x4x512] in place, cos_sin f32[token x64 x2]", launch_rope<512, 128, 4>},
+
     // ---- head_dim 128, GQA 2, kv heads = groups[0] ------------------------------------------------------
     {"attn_decode_paged_q8kv_d128", {160, 1, 1}, 8, 12,
      "q f16[m_q x H x128], k_quants i8[row x KV x128], k_scales f16[row x KV x4], v_quants, v_scales, page_table u32, "
@@ -111,6 +122,15 @@ const KernelEntry REGISTRY[] = {
     {"kv_append_paged_q8_d128", {256, 1, 1}, 5, 8,
      "src f16[n x row_len], scales f16, quants i8, page_table u32, step | push {row_len u32, page u32} | row via page table from step[0]+token",
      launch_kv_append_paged_q8_d128},
+    {"attn_norm_rope_d128", {256, 1, 1}, 4, 12,
+     "x f16[token x n_heads x128], w f32[128], cos_sin f32[token x rot/2 x2], y f16 | push {n_heads u32, rot_dims u32, plus_one u32} | "
+     "RMS norm per head, then rotate-half RoPE of the first rot_dims/2 pairs (i, i+64); rounds to f16 after each, like the two-kernel chain",
+     launch_norm_rope_d128},
+    {"kv_norm_rope_append_paged_q8_d128", {256, 1, 1}, 10, 16,
+     "k_raw f16[n x row_len], v_raw, k_w f32[128], cos_sin f32[n x rot/2 x2], k_scales, k_quants, v_scales, v_quants, page_table u32, step | "
+     "push {row_len u32, page u32, rot_dims u32, plus_one u32} | K: norm(k_w) + RoPE, V: weightless norm; both Q8_0-quantised into row "
+     "page_table[t/page]*page + t%page, t = step[0] + token",
+     launch_kv_norm_rope_append_paged_q8_d128},
     {"kv_dequant_paged_q8_d128", {256, 1, 1}, 5, 8,
      "scales f16, quants i8, page_table u32, dst f16[rows x row_len], step | push {row_len, page} | first step[2] tokens, gathered to linear f16",
      launch_kv_dequant_paged_q8_d128},

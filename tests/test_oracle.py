@@ -290,3 +290,33 @@ def test_multi_query_decode_and_two_level_combine():
     r1 = O.reduce_f32(np.ascontiguousarray(p[:, 3:]), hd, 3, out_mode=1)
     two = O.reduce_f32(np.ascontiguousarray(np.stack([r0, r1], axis=1)), hd, 2).reshape(m_q, N_Q, hd)
     assert np.allclose(two, got, rtol=2e-6, atol=1e-7)
+
+
+# ---- pre-attention steps: known answers for the f64 restatement of reference/mod.rs:156-216 ---------------
+def test_rmsnorm_known_answers():
+    w = np.arange(1, 257, dtype=np.float32)
+    assert np.allclose(O.rmsnorm_f64(np.full(256, 3.0, np.float32), w, 256), w, rtol=1e-6)  # a constant row normalises to 1
+    assert np.allclose(O.rmsnorm_f64(np.full(256, -2.0, np.float32), w, 256, plus_one=True), -(1 + w), rtol=1e-6)
+    x = np.zeros(512, np.float32)
+    x[5] = 4.0  # mean square 16/512 -> inv = sqrt(32)
+    assert np.isclose(O.rmsnorm_f64(x, np.ones(512, np.float32), 512)[5], 4.0 * np.sqrt(32.0), rtol=1e-4)  # up to the 1e-6 epsilon
+    assert np.all(O.rmsnorm_f64(np.zeros(256, np.float32), w, 256) == 0)  # eps keeps the zero row finite
+
+
+def test_rope_known_answers():
+    f = O.inv_freqs(128, 1e6)
+    assert f[0] == 1.0 and np.isclose(f[-1], 1e6 ** (-126 / 128))
+    cs0 = O.cos_sin_table(f, 0, 1).reshape(-1, 2)
+    assert np.all(cs0[:, 0] == 1) and np.all(cs0[:, 1] == 0)
+    x = O.Rng(5).f32_vec(2 * 4 * 512)
+    assert np.array_equal(O.rope_f64(x, 512, 128, 4, O.cos_sin_table(f, 0, 2))[:4 * 512], x[:4 * 512])  # position 0 is the identity
+    y = O.rope_f64(x, 512, 128, 4, O.cos_sin_table(f, 1000, 2)).reshape(-1, 512)
+    xx = x.reshape(-1, 512)
+    assert np.allclose((y ** 2).sum(1), (xx ** 2).sum(1), rtol=1e-5)  # a rotation keeps the norm
+    assert np.array_equal(y[:, 64:256], xx[:, 64:256]) and np.array_equal(y[:, 320:], xx[:, 320:])  # frozen pairs
+    # quarter turn on pair 0 (inv_freq 1): pos = pi/2 is not an integer, so build the table by hand
+    cs = np.zeros((1, 64, 2), np.float32)
+    cs[:, :, 0] = 1.0
+    cs[0, 0] = (0.0, 1.0)
+    r = O.rope_f64(np.arange(512, dtype=np.float32), 512, 128, 1, cs.reshape(-1))
+    assert r[0] == -256.0 and r[256] == 0.0 and r[1] == 1.0
