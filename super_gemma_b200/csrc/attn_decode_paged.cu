@@ -352,8 +352,17 @@ __global__ void __launch_bounds__(WPC * 32, MIN_CTAS)
         const uint32_t pt0 = movmatrix_trans(pack_half2(p00, p01));
         const uint32_t pt1 = movmatrix_trans(pack_half2(p10, p11));
         const uint32_t vs_base = smem_u32(sm.vs[warp][st]) + vsc_off;
-        const uint2 va = lds_u2(vs_base), vb = lds_u2(vs_base + 16);              // tokens 2*t4, 2*t4+1
-        const uint2 vc = lds_u2(vs_base + 8 * 16), vd = lds_u2(vs_base + 9 * 16);  // tokens 8+2*t4, 9+2*t4
+        uint2 va = lds_u2(vs_base), vb = lds_u2(vs_base + 16);              // tokens 2*t4, 2*t4+1
+        uint2 vc = lds_u2(vs_base + 8 * 16), vd = lds_u2(vs_base + 9 * 16);  // tokens 8+2*t4, 9+2*t4
+        if (tok0 + STAGE_TOK > (int)kv_len) {
+            // Rows past the end of the sequence hold whatever was there before; their p is 0, but 0 times a
+            // stale scale that happens to be inf or NaN would not be.
+            const uint2 zero = make_uint2(0u, 0u);
+            if (tok0 + 2 * t4 >= (int)kv_len) va = zero;
+            if (tok0 + 2 * t4 + 1 >= (int)kv_len) vb = zero;
+            if (tok0 + 8 + 2 * t4 >= (int)kv_len) vc = zero;
+            if (tok0 + 9 + 2 * t4 >= (int)kv_len) vd = zero;
+        }
 #pragma unroll
         for (int b = 0; b < 4; b++) {
             // (scale_b of token A, scale_b of token B) as a half2, times (p_A, p_B)

@@ -159,7 +159,8 @@ __global__ void __launch_bounds__(CODEC_THREADS) kv_append_q8_kernel(const __hal
     store_quants(quants, dblk, packed);
 }
 
-// Gather + dequantise the first kv_len logical tokens of a paged Q8_0 pool into linear f16 rows:
+// Gather + dequantise the first kv_len logical tokens of a paged Q8_0 pool into linear f16 rows (and zero
+// the rows up to the next multiple of 64):
 // dst[t][j] = f16(scale * q) read at row page_table[t / page] * page + t % page.  The dequantised
 // value is the one attn_prefill_global_flash_sp_q8.wgsl:100-104 builds in its LDS slab.
 __global__ void __launch_bounds__(CODEC_THREADS) kv_dequant_paged_kernel(const __half* __restrict__ scales,
@@ -173,10 +174,18 @@ __global__ void __launch_bounds__(CODEC_THREADS) kv_dequant_paged_kernel(const _
 {
     const uint32_t hb_per_row = row_len / 16;
     const size_t kv_len = step[STEP_KV_LEN_GLOBAL];
-    const size_t n_rows = kv_len < dst_rows ? kv_len : dst_rows;
+    // The flash kernel reads whole 64-key tiles and masks what lies past kv_len; a masked key weighs 0, but
+    // 0 times a stale inf or NaN would not be 0, so the rest of the last tile is zeroed here.
+    const size_t padded = (kv_len + 63) / 64 * 64;
+    const size_t n_rows = padded < dst_rows ? padded : dst_rows;
     for (size_t i = (size_t)blockIdx.x * CODEC_THREADS + threadIdx.x; i < n_rows * hb_per_row;
          i += (size_t)gridDim.x * CODEC_THREADS) {
         const size_t t = i / hb_per_row, hb = i % hb_per_row;
+        if (t >= kv_len) {
+            uint4* out = reinterpret_cast<uint4*>(dst + t * row_len) + hb * 2;
+            out[0] = out[1] = make_uint4(0u, 0u, 0u, 0u);
+            continue;
+        }
         const size_t p = t / page;
         if (p >= table_len) {
             report_error(status, DEV_ERR_BOUNDS, 104, (uint32_t)p, table_len);

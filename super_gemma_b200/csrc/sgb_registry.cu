@@ -132,7 +132,7 @@ const KernelEntry REGISTRY[] = {
      "page_table[t/page]*page + t%page, t = step[0] + token",
      launch_kv_norm_rope_append_paged_q8_d128},
     {"kv_dequant_paged_q8_d128", {256, 1, 1}, 5, 8,
-     "scales f16, quants i8, page_table u32, dst f16[rows x row_len], step | push {row_len, page} | first step[2] tokens, gathered to linear f16",
+     "scales f16, quants i8, page_table u32, dst f16[rows x row_len], step | push {row_len, page} | first step[2] tokens, gathered to linear f16; rows up to the next multiple of 64 zeroed",
      launch_kv_dequant_paged_q8_d128},
 };
 

@@ -120,11 +120,12 @@ def test_kv_dequant_paged_gathers_to_linear(ctx):
     pool = q8_pool(normal_f16(6, n_tokens, n_kv, 128), table_h, page, pool_pages=7)
     scales, quants = ctx.buffer_from_iter(pool.scales), ctx.buffer_from_iter(pool.quants)
     table = ctx.buffer_from_iter(table_h)
-    dst = ctx.buffer_from_iter(np.full(320 * n_kv * 128, 0x7E00, np.uint16))
+    dst = ctx.buffer_from_iter(np.full(400 * n_kv * 128, 0x7E00, np.uint16))
     step = ctx.new_step_buffer()
     sg.StepState(kv_len_global=n_tokens).write_to(step)
     k = ctx.load_kernel("kv_dequant_paged_q8_d128")
     ctx.dispatch_blocking(k, bind(scales, quants, table, dst, step), (n_kv * 128, page), [1, 1, 1])
-    got = dst.read().reshape(320, n_kv, 128)
+    got = dst.read().reshape(400, n_kv, 128)
     assert np.array_equal(O.f16_bits_to_f32(got[:n_tokens]), pool.deq16)
-    assert np.all(got[n_tokens:] == 0x7E00)  # rows past kv_len are left alone
+    assert np.all(got[n_tokens:320] == 0)  # the rest of the last 64-key tile is zeroed: the flash kernel reads it under a mask
+    assert np.all(got[320:] == 0x7E00)  # rows beyond that are left alone
