@@ -38,6 +38,11 @@ SCALE = 1.0 / math.sqrt(D)
 SEED = 0x5605
 
 
+# dram__bytes_read.sum + dram__bytes_write.sum of one flash_prefill_kernel launch, from an ncu capture of this
+# script (profiles/flash_prefill_kernel__headline_5a.md), keyed by (m, ctx, n_gpus).  Other shapes: not captured.
+FLASH_DRAM_BYTES = {(4096, 131072, 1): 1358588672 + 123469312}
+
+
 def peaks():
     """Measured denominators (driver-written MEASURED_PEAKS.json), else the pool's earlier measurement."""
     p = os.path.join(ROOT, "MEASURED_PEAKS.json")
@@ -334,6 +339,66 @@ def run_decode(dev, rank, world, steps, warmup, dist, ctx_len, m_q, n_splits, se
             "kernel_gbs": (algo / world) / kern_us / 1e3, "algorithmic_bytes": algo, "n_splits": n_splits, "launches": launches}
 
 
+def run_decode_block(dev, steps, warmup, ctx_len, n_splits, seed, chunk=4096):
+    """The whole attention block of one decode token, recorded once and replayed: norm + RoPE of q, the
+    fused norm + RoPE + Q8_0 quantise + paged append of k and v, split-K decode over the ctx_len-token
+    cache, combine.  Also times the fused append alone on a prefill chunk of `chunk` tokens."""
+    torch = dev.torch
+    n_pages = ctx_len // PAGE
+    kq, ks, vq, vs, table = build_paged_kv(dev, seed, ctx_len, list(range(KV)), fisher_yates(seed + 0x100, n_pages), n_pages)
+    g = torch.Generator(device=dev.device)
+    g.manual_seed(seed)
+    rnd = lambda *shape: torch.randn(*shape, generator=g, device=dev.device, dtype=torch.float32)
+    q_raw, k_raw, v_raw = rnd(1, H, D).half(), rnd(chunk, KV, D).half(), rnd(chunk, KV, D).half()
+    q_w, k_w = rnd(D) + 1.0, rnd(D) + 1.0
+    pos = torch.arange(chunk, device=dev.device, dtype=torch.float64)[:, None] + float(ctx_len - 1)
+    ang = pos * torch.pow(torch.tensor(1e6, dtype=torch.float64, device=dev.device),
+                          -2.0 * torch.arange(D // 2, device=dev.device, dtype=torch.float64) / D)[None, :]
+    cos_sin = torch.stack([torch.cos(ang), torch.sin(ang)], dim=-1).float().contiguous()  # host-filled in the reference; values only
+    q = torch.zeros(H * D, dtype=torch.float16, device=dev.device)
+    part = torch.zeros(H * n_splits * (D + 2), dtype=torch.float32, device=dev.device)
+    out = torch.zeros(H * D, dtype=torch.float32, device=dev.device)
+    step_t = torch.tensor([ctx_len - 1, 0, ctx_len, 0], dtype=torch.int32, device=dev.device)  # the token lands in the last row
+    k1, v1 = k_raw[:1].contiguous(), v_raw[:1].contiguous()
+    torch.cuda.synchronize()
+    W = dev.wrap
+    b = {n: W(t) for n, t in dict(q_raw=q_raw, k1=k1, v1=v1, q_w=q_w, k_w=k_w, cs=cos_sin, q=q, part=part, out=out, step=step_t, kq=kq, ks=ks,
+                                  vq=vq, vs=vs, table=table).items()}
+    nr, fused = dev.kernel("attn_norm_rope_d128"), dev.kernel("kv_norm_rope_append_paged_q8_d128")
+    dec, red = dev.kernel("attn_decode_paged_q8kv_d128"), dev.kernel("attn_reduce_f32_d128")
+    row = KV * D
+
+    def step(timer, base):
+        if timer is not None:
+            timer.stamp(base)
+        dev.ctx.dispatch(nr, dev.bind(b["q_raw"], b["q_w"], b["cs"], b["q"]), (H, D, 0), [1, 1, 1])
+        dev.ctx.dispatch(fused, dev.bind(b["k1"], b["v1"], b["k_w"], b["cs"], b["ks"], b["kq"], b["vs"], b["vq"], b["table"], b["step"]),
+                         (row, PAGE, D, 0), [1, 1, 1])
+        dev.ctx.dispatch(dec, dev.bind(b["q"], b["kq"], b["ks"], b["vq"], b["vs"], b["table"], b["part"], b["step"]), (n_splits, SCALE, PAGE),
+                         [KV, n_splits, 1])
+        dev.ctx.dispatch(red, dev.bind(b["part"], b["out"]), n_splits, [H, 1, 1])
+
+    total_s, _, launches = timed(dev, step, steps, warmup, None, stamps_per_step=1, graph=True)
+    res = {"us_per_token": total_s / steps * 1e6, "launches": launches, "kernels_per_token": 4, "ctx": ctx_len, "n_splits": n_splits,
+           "note": "one cache copy: parts of the 143 MB stream may be served from the 126 MB L2"}
+    # the fused append alone, on a prefill chunk written at positions 0..chunk-1
+    step0 = torch.zeros(4, dtype=torch.int32, device=dev.device)
+    b_k, b_v, b_s0 = W(k_raw), W(v_raw), W(step0)
+    torch.cuda.synchronize()
+
+    def step_app(timer, base):
+        if timer is not None:
+            timer.stamp(base)
+        dev.ctx.dispatch(fused, dev.bind(b_k, b_v, b["k_w"], b["cs"], b["ks"], b["kq"], b["vs"], b["vq"], b["table"], b_s0), (row, PAGE, D, 0),
+                         [1, 1, 1])
+
+    total_s, _, _ = timed(dev, step_app, steps, warmup, None, stamps_per_step=1, graph=True)
+    algo = chunk * KV * (2 * D * 2 + 2 * (D + 8))
+    res["fused_append_chunk"] = {"tokens": chunk, "us": total_s / steps * 1e6, "algorithmic_bytes": algo,
+                                 "gbs": algo * steps / total_s / 1e9, "note": "50 MB working set: L2-resident, not an HBM figure"}
+    return res
+
+
 # --------------------------------------------------------------------------------------------------
 # CPU arm: the oracle's f32 shader-order flash prefill on a bounded sample of the headline workload
 # --------------------------------------------------------------------------------------------------
@@ -478,6 +543,8 @@ def main():
                 d4["hbm_frac_kernel"] = d4["kernel_gbs"] / pk["hbm_gbs"]
                 extra["config4_verify_64k"] = d4
                 torch.cuda.empty_cache()
+                extra["decode_block_32k"] = run_decode_block(dev, 40, 5, 32768, 64, 0x5606)
+                torch.cuda.empty_cache()
             d5 = run_decode(dev, rank, world, 40, 5, dist, 131072, 1, 64 if world < 4 else 32, 0x5605, copies=2)
             d5["hbm_frac_kernel"] = d5["kernel_gbs"] / pk["hbm_gbs"]
             extra["config5b_decode_128k"] = d5
@@ -502,7 +569,8 @@ def main():
             "config": workload_config(args, world),
             "roofline": {"bound": "tensor", "kernel": "flash_prefill_kernel (attn_prefill_flash_f16_d128)", "achieved": achieved,
                          "peak": peak, "unit": "TFLOP/s", "frac": achieved / peak,
-                         "peak_kind": f"{pk['kind']} bf16 {'sustained' if long_run else 'burst'}", "traffic": None,
+                         "peak_kind": f"{pk['kind']} bf16 {'sustained' if long_run else 'burst'}",
+                         "traffic": FLASH_DRAM_BYTES.get((args.m, args.ctx, world)),
                          "ms_per_launch": head["flash_ms"], "dequant_ms_per_step": head["dequant_ms"]},
             "cpu_baseline": cpu, "e2e": head.get("e2e"), "gpu_launches": int(head["launches"]), "clocks": clk, "extra": extra,
         }
