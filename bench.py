@@ -39,7 +39,7 @@ SEED = 0x5605
 
 
 # dram__bytes_read.sum + dram__bytes_write.sum of one flash_prefill_kernel launch, from an ncu capture of this
-# script (profiles/flash_prefill_kernel__headline_5a.md), keyed by (m, ctx, n_gpus).  Other shapes: not captured.
+# script (summarised under profiles/), keyed by (m, ctx, n_gpus).  Other shapes: not captured.
 FLASH_DRAM_BYTES = {(4096, 131072, 1): 1358588672 + 123469312}
 
 
@@ -469,7 +469,7 @@ def reference_arm(args):
     line = {"impl": "reference", "metric": "prefill_attn_tflops", "value": v, "unit": "TFLOP/s", "n_gpus": args.gpus,
             "steps": args.steps, "warmup": args.warmup, "ms_per_step": dt / args.steps * 1e3, "higher_is_better": True,
             "scaling": "strong", "vs_baseline": None, "dtype": "f32", "data": "synthetic",
-            "config": workload_config(args, 1), "cpu_baseline": base,
+            "config": workload_config(args, max(1, args.gpus)), "cpu_baseline": base,  # the arm it is compared with
             "e2e": {"value": v, "unit": "TFLOP/s", "h2d_bytes_per_step": 0, "d2h_bytes_per_step": 0}}
     print(json.dumps(line), flush=True)
 
