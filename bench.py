@@ -335,8 +335,34 @@ def run_decode(dev, rank, world, steps, warmup, dist, ctx_len, m_q, n_splits, se
     kv_bytes = ctx_len * KV * (D + 8) * 2  # quants + scales, K and V
     algo = kv_bytes + m_q * H * D * 2 + m_q * H * D * 4 + (ctx_len // PAGE) * 4
     kern_us = float(np.median(deltas[:, 0])) * 1e-3
-    return {"us_per_step": total_s / steps * 1e6, "gbs": algo * steps / total_s / 1e9, "kernel_us": kern_us,
-            "kernel_gbs": (algo / world) / kern_us / 1e3, "algorithmic_bytes": algo, "n_splits": n_splits, "launches": launches}
+    res = {"us_per_step": total_s / steps * 1e6, "gbs": algo * steps / total_s / 1e9, "kernel_us": kern_us,
+           "kernel_gbs": (algo / world) / kern_us / 1e3, "algorithmic_bytes": algo, "n_splits": n_splits, "launches": launches}
+    if world > 1:
+        # The same step with the combine and the exchange in ONE kernel over peer memory (attn_reduce_exchange_d128)
+        # instead of reduce + NCCL all-gather + combine; no collective call, so it replays as a CUDA graph.
+        try:
+            from super_gemma_b200 import sharding
+
+            xbuf, peers, keep = sharding.alloc_exchange(dist, dev.device, world, rank, rows)
+            b_x, b_peers = W(xbuf), W(peers)
+            fx = dev.kernel("attn_reduce_exchange_d128")
+
+            def step_fused(timer, base):
+                kq, ks, vq, vs, tab = b_pools[base % len(b_pools)]
+                if timer is not None:
+                    timer.stamp(base)
+                dev.ctx.dispatch(dec, dev.bind(b_q, kq, ks, vq, vs, tab, b_part, b_step), (n_splits, SCALE, PAGE), [KV, n_splits, m_q])
+                if timer is not None:
+                    timer.stamp(base + 1)
+                dev.ctx.dispatch(fx, dev.bind(b_part, b_x, b_peers, b_out), (n_splits, world, rank), [rows, 1, 1])
+
+            total_f, _, launches_f = timed(dev, step_fused, steps, warmup, dist, stamps_per_step=2, graph=True)
+            res.update({"nccl_us_per_step": res["us_per_step"], "nccl_gbs": res["gbs"], "us_per_step": total_f / steps * 1e6,
+                        "gbs": algo * steps / total_f / 1e9, "launches": launches_f,
+                        "exchange": f"one kernel, peer stores over NVLink ({keep[1]}); nccl_* = reduce + all-gather + combine"})
+        except Exception as e:
+            res["fused_exchange_error"] = repr(e)
+    return res
 
 
 def run_decode_block(dev, steps, warmup, ctx_len, n_splits, seed, chunk=4096):

@@ -75,6 +75,9 @@ int launch_combine_ranks_d128(const LaunchArgs&);
 template <int HD, int G, int WINDOW, int RING, int TWO_RANGE, int OUT_F32> int launch_prefill_generic(const LaunchArgs&);
 int launch_prefill_paged_q8kv_scalar_d128(const LaunchArgs&);
 
+// attn_exchange.cu
+int launch_reduce_exchange_d128(const LaunchArgs&);
+
 // attn_decode_paged.cu
 int launch_decode_paged_q8kv_d128(const LaunchArgs&);
 

@@ -122,6 +122,11 @@ const KernelEntry REGISTRY[] = {
     {"kv_append_paged_q8_d128", {256, 1, 1}, 5, 8,
      "src f16[n x row_len], scales f16, quants i8, page_table u32, step | push {row_len u32, page u32} | row via page table from step[0]+token",
      launch_kv_append_paged_q8_d128},
+    {"attn_reduce_exchange_d128", {128, 1, 1}, 4, 12,
+     "part f32[rows x n_splits x 130], xbuf (this rank's exchange buffer: f32[2][world][rows][130], u32[2][world][rows], u32[rows], zeroed once), "
+     "peers u64[world] (every rank's xbuf, rank order), out f32[rows x128] | push {n_splits u32, world u32, rank u32} | grid [rows]; "
+     "merges the local splits, stores the row into every rank's buffer over NVLink, waits (bounded) for all ranks' rows, merges in rank order",
+     launch_reduce_exchange_d128},
     {"attn_norm_rope_d128", {256, 1, 1}, 4, 12,
      "x f16[token x n_heads x128], w f32[128], cos_sin f32[token x rot/2 x2], y f16 | push {n_heads u32, rot_dims u32, plus_one u32} | "
      "RMS norm per head, then rotate-half RoPE of the first rot_dims/2 pairs (i, i+64); rounds to f16 after each, like the two-kernel chain",

@@ -72,3 +72,52 @@ def combine_ranks(gathered: np.ndarray) -> np.ndarray:
         acc += w[r][:, None] * g[r, :, :hd]
         l += w[r] * g[r, :, hd + 1]
     return acc / l[:, None]
+
+
+# ---- the fused combine + exchange of sequence-parallel decode (attn_reduce_exchange_d128) ------------------
+def exchange_words(world: int, rows: int, hd: int = 128) -> int:
+    """4-byte words of one rank's exchange buffer: data f32[2][world][rows][hd + 2], flags u32[2][world][rows],
+    epoch u32[rows]."""
+    return 2 * world * rows * (hd + 2) + 2 * world * rows + rows
+
+
+def alloc_exchange(dist, device, world: int, rank: int, rows: int):
+    """Allocate the zeroed exchange buffer of this rank so that every rank of `dist`'s world can store into it,
+    and return (buffer tensor, int64 tensor of all ranks' buffer addresses as seen from this GPU, keep-alive).
+    Peer mappings come from torch's symmetric memory when the platform offers it, else from CUDA IPC
+    handles.  Plain peer memory only: no multicast object is asked for."""
+    import os
+
+    import torch
+
+    words = exchange_words(world, rows)
+    keep = []
+    try:
+        os.environ.setdefault("TORCH_SYMM_MEM_DISABLE_MULTICAST", "1")
+        import torch.distributed._symmetric_memory as symm_mem
+
+        buf = symm_mem.empty(words, dtype=torch.float32, device=device)
+        hdl = symm_mem.rendezvous(buf, dist.group.WORLD)
+        ptrs = [int(p) for p in hdl.buffer_ptrs]
+        keep.append(hdl)
+        how = "symmetric memory"
+    except Exception:
+        buf = torch.zeros(words, dtype=torch.float32, device=device)
+        handle = buf.untyped_storage()._share_cuda_()
+        handles = [None] * world
+        dist.all_gather_object(handles, handle)
+        ptrs = []
+        for r, h in enumerate(handles):
+            if r == rank:
+                ptrs.append(buf.data_ptr())
+                continue
+            storage = torch.UntypedStorage._new_shared_cuda(*h)
+            peer = torch.empty(0, dtype=torch.float32, device=device).set_(storage)
+            keep.append(peer)
+            ptrs.append(peer.data_ptr())
+        how = "CUDA IPC"
+    buf.zero_()
+    torch.cuda.synchronize()
+    dist.barrier()  # nobody stores into a buffer that its owner has not zeroed yet
+    peers = torch.tensor(ptrs, dtype=torch.int64, device=device)
+    return buf, peers, (keep, how)

@@ -1,0 +1,65 @@
+"""attn_reduce_exchange_d128: the split-K combine fused with the exchange between the ranks of a
+sequence-parallel decode.  On one GPU the exchange is with itself and must reproduce attn_reduce_f32_d128 bit
+for bit, step after step (alternating slots, epochs); with two or more GPUs a worker per rank checks the
+kernel against reduce + NCCL all-gather + rank-ordered combine."""
+import os
+import subprocess
+import sys
+
+import numpy as np
+import pytest
+
+from cases import D, bind
+
+pytestmark = pytest.mark.gpu
+
+ROOT = os.path.dirname(os.path.dirname(os.path.abspath(__file__)))
+
+
+def test_single_rank_exchange_equals_plain_reduce():
+    import super_gemma_b200 as sg
+    from super_gemma_b200 import sharding
+
+    ctx = sg.GpuContext(0)
+    rows, n_splits = 32, 9
+    xbuf = ctx.new_buffer(sharding.exchange_words(1, rows), np.float32)  # zero-initialised
+    peers = ctx.buffer_from_iter(np.array([xbuf.device_ptr], np.uint64))
+    red, fused = ctx.load_kernel("attn_reduce_f32_d128"), ctx.load_kernel("attn_reduce_exchange_d128")
+    rng = np.random.default_rng(9)
+    for step in range(5):
+        part = rng.standard_normal((rows, n_splits, D + 2)).astype(np.float32)
+        part[:, :, D + 1] = np.abs(part[:, :, D + 1]) + 0.25
+        part[:, 7:, D], part[:, 7:, D + 1], part[:, 7:, :D] = -3.0e38, 0.0, 0.0  # empty splits
+        p = ctx.buffer_from_iter(part.reshape(-1))
+        want, got = ctx.new_buffer(rows * D, np.float32), ctx.new_buffer(rows * D, np.float32)
+        ctx.dispatch_blocking(red, bind(p, want), n_splits, [rows, 1, 1])
+        ctx.dispatch_blocking(fused, bind(p, xbuf, peers, got), (n_splits, 1, 0), [rows, 1, 1])
+        assert np.array_equal(got.read().view(np.uint32), want.read().view(np.uint32)), f"step {step}"
+    words = xbuf.read().view(np.uint32)
+    assert np.all(words[-rows:] == 5)  # the per-row epoch counts the launches
+
+
+def test_rejects_bad_arguments():
+    import super_gemma_b200 as sg
+
+    ctx = sg.GpuContext(0)
+    k = ctx.load_kernel("attn_reduce_exchange_d128")
+    small = ctx.new_buffer(64, np.float32)
+    part = ctx.new_buffer(32 * 2 * (D + 2), np.float32)
+    out = ctx.new_buffer(32 * D, np.float32)
+    peers = ctx.new_buffer(1, np.uint64)
+    with pytest.raises(sg.Validation):
+        ctx.dispatch_blocking(k, bind(part, small, peers, out), (2, 1, 0), [32, 1, 1])  # exchange buffer too small
+    with pytest.raises(sg.Validation):
+        ctx.dispatch_blocking(k, bind(part, small, peers, out), (2, 2, 2), [32, 1, 1])  # rank outside the world
+
+
+def test_two_ranks_match_the_nccl_path():
+    import torch
+
+    if torch.cuda.device_count() < 2:
+        pytest.skip("needs two GPUs")
+    cmd = [sys.executable, "-m", "torch.distributed.run", "--nnodes=1", "--nproc-per-node", "2", "--master-addr", "127.0.0.1",
+           "--master-port", "29533", os.path.join(ROOT, "tests", "exchange_worker.py")]
+    r = subprocess.run(cmd, capture_output=True, text=True, timeout=300, cwd=ROOT)
+    assert r.returncode == 0 and "exchange worker: OK" in r.stdout, r.stdout[-2000:] + r.stderr[-2000:]
