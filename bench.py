@@ -366,8 +366,8 @@ def run_decode(dev, rank, world, steps, warmup, dist, ctx_len, m_q, n_splits, se
 
 
 def run_decode_block(dev, steps, warmup, ctx_len, n_splits, seed, chunk=4096):
-    """The whole attention block of one decode token, recorded once and replayed: norm + RoPE of q, the
-    fused norm + RoPE + Q8_0 quantise + paged append of k and v, split-K decode over the ctx_len-token
+    """The whole attention block of one decode token, recorded once and replayed: one launch for norm + RoPE
+    of q and norm + RoPE + Q8_0 quantise + paged append of k and v, split-K decode over the ctx_len-token
     cache, combine.  Also times the fused append alone on a prefill chunk of `chunk` tokens."""
     torch = dev.torch
     n_pages = ctx_len // PAGE
@@ -390,22 +390,21 @@ def run_decode_block(dev, steps, warmup, ctx_len, n_splits, seed, chunk=4096):
     W = dev.wrap
     b = {n: W(t) for n, t in dict(q_raw=q_raw, k1=k1, v1=v1, q_w=q_w, k_w=k_w, cs=cos_sin, q=q, part=part, out=out, step=step_t, kq=kq, ks=ks,
                                   vq=vq, vs=vs, table=table).items()}
-    nr, fused = dev.kernel("attn_norm_rope_d128"), dev.kernel("kv_norm_rope_append_paged_q8_d128")
+    qkv, fused = dev.kernel("qkv_norm_rope_append_paged_q8_d128"), dev.kernel("kv_norm_rope_append_paged_q8_d128")
     dec, red = dev.kernel("attn_decode_paged_q8kv_d128"), dev.kernel("attn_reduce_f32_d128")
     row = KV * D
 
     def step(timer, base):
         if timer is not None:
             timer.stamp(base)
-        dev.ctx.dispatch(nr, dev.bind(b["q_raw"], b["q_w"], b["cs"], b["q"]), (H, D, 0), [1, 1, 1])
-        dev.ctx.dispatch(fused, dev.bind(b["k1"], b["v1"], b["k_w"], b["cs"], b["ks"], b["kq"], b["vs"], b["vq"], b["table"], b["step"]),
-                         (row, PAGE, D, 0), [1, 1, 1])
+        dev.ctx.dispatch(qkv, dev.bind(b["q_raw"], b["q_w"], b["q"], b["k1"], b["v1"], b["k_w"], b["cs"], b["ks"], b["kq"], b["vs"], b["vq"],
+                                       b["table"], b["step"]), (H, row, PAGE, D, 0), [1, 1, 1])
         dev.ctx.dispatch(dec, dev.bind(b["q"], b["kq"], b["ks"], b["vq"], b["vs"], b["table"], b["part"], b["step"]), (n_splits, SCALE, PAGE),
                          [KV, n_splits, 1])
         dev.ctx.dispatch(red, dev.bind(b["part"], b["out"]), n_splits, [H, 1, 1])
 
     total_s, _, launches = timed(dev, step, steps, warmup, None, stamps_per_step=1, graph=True)
-    res = {"us_per_token": total_s / steps * 1e6, "launches": launches, "kernels_per_token": 4, "ctx": ctx_len, "n_splits": n_splits,
+    res = {"us_per_token": total_s / steps * 1e6, "launches": launches, "kernels_per_token": 3, "ctx": ctx_len, "n_splits": n_splits,
            "note": "one cache copy: parts of the 143 MB stream may be served from the 126 MB L2"}
     # the fused append alone, on a prefill chunk written at positions 0..chunk-1
     step0 = torch.zeros(4, dtype=torch.int32, device=dev.device)

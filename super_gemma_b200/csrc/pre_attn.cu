@@ -196,15 +196,34 @@ __device__ __forceinline__ void quant_block_f32(const float (&x)[32], __half& sc
 
 // kv_norm_rope_append_paged_q8_d128: blocks [0, n) are K (norm with k_w, rope), blocks [n, 2n) are V (weightless
 // norm); each lands Q8_0-quantised at row page_table[t / page] * page + t % page, t = step[0] + token.
+// qkv_norm_rope_append_paged_q8_d128 adds nq blocks for Q after them, from the next warp boundary on (norm with
+// q_w, rope, f16 out): the whole pre-attention step of a layer in one launch.
 template <bool PLUS_ONE>
 __global__ void __launch_bounds__(PRE_THREADS)
-    kv_norm_rope_append_kernel(const __half* __restrict__ k_raw, const __half* __restrict__ v_raw, const float* __restrict__ k_w,
+    kv_norm_rope_append_kernel(const __half* __restrict__ q_raw, const float* __restrict__ q_w, __half* __restrict__ q_out,
+                               uint32_t n_q, size_t nq_blocks,
+                               const __half* __restrict__ k_raw, const __half* __restrict__ v_raw, const float* __restrict__ k_w,
                                const float2* __restrict__ cos_sin, __half* __restrict__ k_scales, int8_t* __restrict__ k_quants,
                                __half* __restrict__ v_scales, int8_t* __restrict__ v_quants, const uint32_t* __restrict__ page_table,
                                uint32_t table_len, uint32_t page, const uint32_t* __restrict__ step, uint32_t n_kv, uint32_t half_rot,
                                size_t n_blocks, size_t dst_rows, uint32_t* status)
 {
     const size_t g = (size_t)blockIdx.x * PRE_THREADS + threadIdx.x;
+    const size_t q_base = (2 * n_blocks + 31) / 32 * 32;  // the Q blocks start on a warp boundary
+    if (g >= q_base) {
+        const size_t blk = g - q_base;
+        const bool q_live = blk < nq_blocks;
+        const size_t row = blk / 4;
+        float v[32];
+        norm_rope_block_d128<PLUS_ONE>(q_raw + row * 128, q_w, cos_sin + (row / n_q) * half_rot, half_rot, (int)(blk % 4), q_live, v);
+        if (!q_live) return;
+        uint4 out[4];
+        pack_f16x32(v, out);
+        uint4* o = reinterpret_cast<uint4*>(q_out + blk * 32);
+#pragma unroll
+        for (int i = 0; i < 4; i++) o[i] = out[i];
+        return;
+    }
     const bool live = g < 2 * n_blocks;  // n_blocks is a multiple of 4: K and V never share a row's four lanes
     const bool is_v = g >= n_blocks;
     const size_t blk = is_v ? g - n_blocks : g;
@@ -243,6 +262,9 @@ struct PushNormRope {
 };
 struct PushKvNormRope {
     uint32_t row_len, page, rot_dims, plus_one;
+};
+struct PushQkvNormRope {
+    uint32_t n_q_heads, row_len, page, rot_dims, plus_one;
 };
 
 }  // namespace
@@ -324,11 +346,46 @@ int launch_kv_norm_rope_append_paged_q8_d128(const LaunchArgs& a)
     if (n_blocks == 0) return 0;
     auto kern = p.plus_one ? kv_norm_rope_append_kernel<true> : kv_norm_rope_append_kernel<false>;
     kern<<<grid_for(2 * n_blocks), PRE_THREADS, 0, a.stream>>>(
+        nullptr, nullptr, nullptr, 1u, (size_t)0,
         (const __half*)a.b[0].ptr, (const __half*)a.b[1].ptr, (const float*)a.b[2].ptr, (const float2*)a.b[3].ptr, (__half*)a.b[4].ptr,
         (int8_t*)a.b[5].ptr, (__half*)a.b[6].ptr, (int8_t*)a.b[7].ptr, (const uint32_t*)a.b[8].ptr, (uint32_t)(a.b[8].bytes / 4), p.page,
         (const uint32_t*)a.b[9].ptr, p.row_len / 128, p.rot_dims / 2, n_blocks, dst_rows, a.status);
     ++*a.launches;
     return check_cuda(a, cudaGetLastError(), "kv_norm_rope_append_paged_q8_d128");
+}
+
+// qkv_norm_rope_append_paged_q8_d128: q_raw f16[n x n_q x128], q_w f32[128], q_out f16, then the ten bindings of
+// kv_norm_rope_append_paged_q8_d128.  push {n_q_heads, row_len, page, rot_dims, plus_one}.
+int launch_qkv_norm_rope_append_paged_q8_d128(const LaunchArgs& a)
+{
+    const PushQkvNormRope p = *(const PushQkvNormRope*)a.push;
+    if (p.n_q_heads == 0 || p.row_len == 0 || p.row_len % 128 || p.page == 0 || p.rot_dims > 128 || p.rot_dims % 2)
+        return fail_validation(a, "qkv_norm_rope_append_paged_q8_d128: n_q_heads > 0, row_len = n_kv_heads*128, page > 0, even rot_dims <= 128");
+    const BufView* kv = a.b + 3;
+    if (kv[0].bytes % (p.row_len * 2) || kv[1].bytes != kv[0].bytes)
+        return fail_validation(a, "qkv_norm_rope_append_paged_q8_d128: k_raw and v_raw must be the same whole rows");
+    const size_t tokens = kv[0].bytes / (p.row_len * 2);
+    if (a.b[0].bytes != tokens * p.n_q_heads * 256) return fail_validation(a, "qkv_norm_rope_append_paged_q8_d128: q_raw must hold the same tokens");
+    if (int r = need_bytes(a, 1, 128 * 4, "q_w")) return r;
+    if (int r = need_bytes(a, 2, a.b[0].bytes, "q_out")) return r;
+    if (int r = need_bytes(a, 5, 128 * 4, "k_w")) return r;
+    if (int r = need_bytes(a, 6, tokens * (p.rot_dims / 2) * 8, "cos_sin")) return r;
+    if (int r = need_bytes(a, 12, 16, "step")) return r;
+    const size_t dst_rows = kv[5].bytes / p.row_len;
+    if (kv[7].bytes / p.row_len != dst_rows) return fail_validation(a, "qkv_norm_rope_append_paged_q8_d128: K and V pools differ in rows");
+    if (kv[4].bytes / 2 < dst_rows * (p.row_len / 32) || kv[6].bytes / 2 < dst_rows * (p.row_len / 32))
+        return fail_validation(a, "qkv_norm_rope_append_paged_q8_d128: scales buffer too short for the quants buffer");
+    const size_t n_blocks = kv[0].bytes / 64, nq_blocks = a.b[0].bytes / 64;
+    if (n_blocks == 0) return 0;
+    const size_t q_base = (2 * n_blocks + 31) / 32 * 32;
+    auto kern = p.plus_one ? kv_norm_rope_append_kernel<true> : kv_norm_rope_append_kernel<false>;
+    kern<<<grid_for(q_base + nq_blocks), PRE_THREADS, 0, a.stream>>>(
+        (const __half*)a.b[0].ptr, (const float*)a.b[1].ptr, (__half*)a.b[2].ptr, p.n_q_heads, nq_blocks, (const __half*)kv[0].ptr,
+        (const __half*)kv[1].ptr, (const float*)kv[2].ptr, (const float2*)kv[3].ptr, (__half*)kv[4].ptr, (int8_t*)kv[5].ptr,
+        (__half*)kv[6].ptr, (int8_t*)kv[7].ptr, (const uint32_t*)kv[8].ptr, (uint32_t)(kv[8].bytes / 4), p.page,
+        (const uint32_t*)kv[9].ptr, p.row_len / 128, p.rot_dims / 2, n_blocks, dst_rows, a.status);
+    ++*a.launches;
+    return check_cuda(a, cudaGetLastError(), "qkv_norm_rope_append_paged_q8_d128");
 }
 
 }  // namespace sgb

@@ -66,6 +66,7 @@ template <int ROW_LEN, int PLUS_ONE> int launch_rmsnorm(const LaunchArgs&);
 template <int HEAD_DIM, int ROT_DIMS, int N_HEADS> int launch_rope(const LaunchArgs&);
 int launch_norm_rope_d128(const LaunchArgs&);
 int launch_kv_norm_rope_append_paged_q8_d128(const LaunchArgs&);
+int launch_qkv_norm_rope_append_paged_q8_d128(const LaunchArgs&);
 
 // attn_generic.cu
 template <int HD, int G, int KFMT, int VFMT, int STEP_SLOT> int launch_decode_generic(const LaunchArgs&);

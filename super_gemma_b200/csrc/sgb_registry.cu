@@ -136,6 +136,11 @@ const KernelEntry REGISTRY[] = {
      "push {row_len u32, page u32, rot_dims u32, plus_one u32} | K: norm(k_w) + RoPE, V: weightless norm; both Q8_0-quantised into row "
      "page_table[t/page]*page + t%page, t = step[0] + token",
      launch_kv_norm_rope_append_paged_q8_d128},
+    {"qkv_norm_rope_append_paged_q8_d128", {256, 1, 1}, 13, 20,
+     "q_raw f16[n x n_q x128], q_w f32[128], q_out f16, then the ten bindings of kv_norm_rope_append_paged_q8_d128 | "
+     "push {n_q_heads u32, row_len u32, page u32, rot_dims u32, plus_one u32} | the whole pre-attention step in one launch: "
+     "q = RoPE(norm(q_raw, q_w)) as f16, and K/V normed, rotated, quantised and appended as by the ten-binding kernel",
+     launch_qkv_norm_rope_append_paged_q8_d128},
     {"kv_dequant_paged_q8_d128", {256, 1, 1}, 5, 8,
      "scales f16, quants i8, page_table u32, dst f16[rows x row_len], step | push {row_len, page} | first step[2] tokens, gathered to linear f16; rows up to the next multiple of 64 zeroed",
      launch_kv_dequant_paged_q8_d128},

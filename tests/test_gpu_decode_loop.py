@@ -1,8 +1,8 @@
 """GPU tests of the whole attention block of a decode step, driven the way the reference's caller drives
 sg-gpu: record once, then per token only write the step words and the token's inputs and replay
 (crates/sg-gpu/src/graph.rs:29-61,523-528; crates/sg-model/src/graph.rs:552-640).  The block is
-norm + RoPE of q, the fused norm + RoPE + quantise + paged append of k and v, split-K decode over the
-paged Q8_0 cache and the combine.  Page tables come from the cache2 manager.  The second test is the
+one launch for norm + RoPE of q and norm + RoPE + quantise + paged append of k and v, split-K decode over
+the paged Q8_0 cache, and the combine.  Page tables come from the cache2 manager.  The second test is the
 speculative step of docs/plans/07-mtp-speculative-decoding.md:23-27,58-59: append K draft tokens, verify
 them in one launch, accept a prefix, and roll back by truncating the lengths."""
 import numpy as np
@@ -94,14 +94,13 @@ def test_recorded_decode_block_replays_across_a_page_boundary(ctx):
     q_d = ctx.new_buffer(N_Q * D, np.uint16)
     part = ctx.new_buffer(N_Q * n_splits * (D + 2), np.float32)
     out = ctx.new_buffer(N_Q * D, np.float32)
-    kernels = [ctx.load_kernel(n) for n in ("attn_norm_rope_d128", "kv_norm_rope_append_paged_q8_d128", "attn_decode_paged_q8kv_d128",
-                                            "attn_reduce_f32_d128")]
+    kernels = [ctx.load_kernel(n) for n in ("qkv_norm_rope_append_paged_q8_d128", "attn_decode_paged_q8kv_d128", "attn_reduce_f32_d128")]
 
     def record(c):
-        c.dispatch(kernels[0], bind(q_raw_d, b.q_w_d, cs_d, q_d), (N_Q, ROT, 0), [1, 1, 1])
-        c.dispatch(kernels[1], bind(k_raw_d, v_raw_d, b.k_w_d, cs_d, b.ks, b.kq, b.vs, b.vq, b.table, b.step), (ROW, PAGE, ROT, 0), [1, 1, 1])
-        c.dispatch(kernels[2], bind(q_d, b.kq, b.ks, b.vq, b.vs, b.table, part, b.step), (n_splits, SCALE, PAGE), [N_KV, n_splits, 1])
-        c.dispatch(kernels[3], bind(part, out), n_splits, [N_Q, 1, 1])
+        c.dispatch(kernels[0], bind(q_raw_d, b.q_w_d, q_d, k_raw_d, v_raw_d, b.k_w_d, cs_d, b.ks, b.kq, b.vs, b.vq, b.table, b.step),
+                   (N_Q, ROW, PAGE, ROT, 0), [1, 1, 1])
+        c.dispatch(kernels[1], bind(q_d, b.kq, b.ks, b.vq, b.vs, b.table, part, b.step), (n_splits, SCALE, PAGE), [N_KV, n_splits, 1])
+        c.dispatch(kernels[2], bind(part, out), n_splits, [N_Q, 1, 1])
 
     graph = ctx.record_graph(record)
     for pos in range(125, 131):  # 127 -> 128 crosses into the third page

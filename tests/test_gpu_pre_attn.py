@@ -159,3 +159,37 @@ def test_fused_kv_append_reports_a_short_table(ctx):
     with pytest.raises(sg.Bounds):
         ctx.dispatch_blocking(ctx.load_kernel("kv_norm_rope_append_paged_q8_d128"), bufs, (row, page, 128, 0), [1, 1, 1])
     ctx.sync()
+
+
+@pytest.mark.parametrize("tokens,n_kv", [(1, 4), (5, 4), (3, 16), (2, 1)])
+def test_one_launch_qkv_equals_the_two_kernels(ctx, tokens, n_kv):
+    """qkv_norm_rope_append_paged_q8_d128 = attn_norm_rope_d128 on q + kv_norm_rope_append_paged_q8_d128, bit for bit
+    (also when the K/V blocks do not end on a warp boundary: n_kv = 1 gives 8 blocks per token)."""
+    import super_gemma_b200 as sg
+
+    n_q, page, pool_pages, rot, pos = 2 * n_kv, 64, 4, 128, 70
+    row = n_kv * 128
+    rng = O.Rng(0x0DE + tokens + n_kv)
+    q_raw, k_raw, v_raw = (O.through_f16(rng.f32_vec(tokens * h * 128)) for h in (n_q, n_kv, n_kv))
+    q_w, k_w = rng.f32_vec(128), rng.f32_vec(128)
+    cs = O.cos_sin_table(O.inv_freqs(rot, 1e6), pos, tokens)
+    up = ctx.buffer_from_iter
+    qr, kr, vr, qw, kw, csb = up(O.f32_to_f16_bits(q_raw)), up(O.f32_to_f16_bits(k_raw)), up(O.f32_to_f16_bits(v_raw)), up(q_w), up(k_w), up(cs)
+    table = up(np.array([2, 0, 3, 1], np.uint32))
+    step = ctx.new_step_buffer()
+    sg.StepState(pos=pos).write_to(step)
+    rows = pool_pages * page
+    mk = lambda dt, n: ctx.new_buffer(n, dt)
+    a = [mk(np.uint16, rows * row // 32), mk(np.int8, rows * row), mk(np.uint16, rows * row // 32), mk(np.int8, rows * row)]
+    b = [mk(np.uint16, rows * row // 32), mk(np.int8, rows * row), mk(np.uint16, rows * row // 32), mk(np.int8, rows * row)]
+    q1, q2 = mk(np.uint16, tokens * n_q * 128), mk(np.uint16, tokens * n_q * 128)
+    ctx.dispatch_blocking(ctx.load_kernel("qkv_norm_rope_append_paged_q8_d128"), bind(qr, qw, q1, kr, vr, kw, csb, *a, table, step),
+                          (n_q, row, page, rot, 0), [1, 1, 1])
+    ctx.dispatch_blocking(ctx.load_kernel("attn_norm_rope_d128"), bind(qr, qw, csb, q2), (n_q, rot, 0), [1, 1, 1])
+    ctx.dispatch_blocking(ctx.load_kernel("kv_norm_rope_append_paged_q8_d128"), bind(kr, vr, kw, csb, *b, table, step), (row, page, rot, 0),
+                          [1, 1, 1])
+    assert np.array_equal(q1.read(), q2.read())
+    assert np.any(q1.read() != 0)
+    for x, y in zip(a, b):
+        assert np.array_equal(x.read(), y.read())
+    assert np.any(a[1].read() != 0)
