@@ -557,7 +557,8 @@ def main():
                                                  "frac_of_burst_peak": c2["flop_total"] / (c2["flash_ms"] * 1e-3) / 1e12 / pk["tf_burst"]}
                 torch.cuda.empty_cache()
                 best = None
-                for ns in (32, 64):
+                # 37 and 74 splits x 16 kv heads make 592 = 148 x 4 CTAs: every SM holds the same number
+                for ns in (32, 37, 64, 74):
                     d3 = run_decode(dev, rank, world, 40, 5, dist, 32768, 1, ns, 0x5603)
                     if best is None or d3["kernel_us"] < best["kernel_us"]:
                         best = d3

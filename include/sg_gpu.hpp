@@ -212,4 +212,53 @@ private:
     uint32_t n_;
 };
 
+// Page tables for the paged kernels: the radix trie of docs/plans/04-kv-cache.md:40-51 at page granularity
+// over a pool of physical pages (constants crates/sg-cache/src/lib.rs:9-13).  Host side only.
+class PageCache {
+public:
+    struct Sequence {
+        uint64_t handle = 0;
+        std::vector<uint32_t> table;  // logical page -> physical page
+        uint64_t reused_tokens = 0;   // K/V of this many leading tokens is already in the pool
+    };
+    static constexpr uint32_t MIN_PAGE_SIZE = 16, MAX_PAGE_SIZE = 512, DEFAULT_PAGE_SIZE = 256;
+
+    explicit PageCache(uint32_t pool_pages, uint32_t page_tokens = DEFAULT_PAGE_SIZE) : page_(page_tokens)
+    {
+        check(sgb_cache2_create(page_tokens, pool_pages, &c_));
+    }
+    PageCache(const PageCache&) = delete;
+    ~PageCache() { sgb_cache2_destroy(c_); }
+
+    uint64_t lookup(const std::vector<int32_t>& tokens)
+    {
+        uint64_t matched = 0;
+        check(sgb_cache2_lookup(c_, tokens.data(), tokens.size(), &matched));
+        return matched;
+    }
+    Sequence acquire(const std::vector<int32_t>& tokens, uint64_t capacity_tokens = 0)
+    {
+        const uint64_t cap = capacity_tokens > tokens.size() ? capacity_tokens : tokens.size();
+        Sequence s;
+        s.table.resize(size_t((cap + page_ - 1) / page_) + 1);
+        uint32_t n_pages = 0;
+        check(sgb_cache2_acquire(c_, tokens.data(), tokens.size(), cap, s.table.data(), uint32_t(s.table.size()), &n_pages,
+                                 &s.reused_tokens, &s.handle));
+        s.table.resize(n_pages);
+        return s;
+    }
+    void commit(const Sequence& s, const std::vector<int32_t>& tokens) { check(sgb_cache2_commit(c_, s.handle, tokens.data(), tokens.size())); }
+    void release(const Sequence& s) { check(sgb_cache2_release(c_, s.handle)); }
+    sgb_cache2_stats_t stats() const
+    {
+        sgb_cache2_stats_t st;
+        check(sgb_cache2_stats(c_, &st));
+        return st;
+    }
+
+private:
+    sgb_cache2* c_ = nullptr;
+    uint32_t page_;
+};
+
 }  // namespace sg_gpu

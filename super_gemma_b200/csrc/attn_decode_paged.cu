@@ -145,6 +145,8 @@ __global__ void __launch_bounds__(WPC * 32, MIN_CTAS)
         for (int i = 0; i < NSTAGES; i++) mbar_init(&sm.full[warp][i], 1);
         mbar_fence_init();
     }
+    pdl_wait();  // everything below reads what earlier kernels of the stream wrote (step words, q, the appended rows)
+    pdl_launch_dependents();
     const uint32_t kv_len = __ldg(step + STEP_KV_LEN_GLOBAL);
     const uint32_t chunk = (kv_len + n_splits - 1) / n_splits;
     const uint32_t t_begin = min((uint32_t)split * chunk, kv_len);
@@ -495,9 +497,8 @@ cudaError_t launch_decode_variant(cudaStream_t stream, int device, const CUtenso
         attr_set[device] = true;
     }
     const uint32_t ctas_x = (n_kv * SUB + WPC - 1) / WPC;
-    decode_paged_kernel<NSTAGES, MIN_CTAS, SUB><<<dim3(ctas_x, n_splits), WPC * 32, smem, stream>>>(
-        tm[0], tm[1], tm[2], tm[3], q, page_table, table_len, page, pool_pages, part, step, n_kv, n_splits, scale, m_q, status);
-    return cudaGetLastError();
+    return launch_dependent(decode_paged_kernel<NSTAGES, MIN_CTAS, SUB>, dim3(ctas_x, n_splits), dim3(WPC * 32), smem, stream, tm[0], tm[1],
+                            tm[2], tm[3], q, page_table, table_len, page, pool_pages, part, step, n_kv, n_splits, scale, m_q, status);
 }
 
 // Shape of the launch.  Three 4.5 KB stages per warp = 54 KB per CTA and 128 registers per thread let

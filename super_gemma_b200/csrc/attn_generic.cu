@@ -248,6 +248,8 @@ __global__ void __launch_bounds__(128) reduce_kernel(const float* __restrict__ p
     __shared__ float red[4];
     const size_t row = blockIdx.x, rows = gridDim.x;
     const int t = threadIdx.x;
+    pdl_wait();  // the partials come from the kernel before this one
+    pdl_launch_dependents();
     const size_t s_stride = split_major ? rows * (HD + 2) : (size_t)(HD + 2);
     const float* base = part + (split_major ? row : row * n_splits) * (HD + 2);
 
@@ -486,9 +488,10 @@ int launch_reduce(const LaunchArgs& a)
     if (int r = need_bytes(a, 0, rows * n_splits * (HD + 2) * 4, "part")) return r;
     const size_t out_bytes = OUT_MODE == 0 ? rows * HD * 2 : OUT_MODE == 1 ? rows * HD * 4 : rows * (HD + 2) * 4;
     if (int r = need_bytes(a, 1, out_bytes, "out")) return r;
-    reduce_kernel<HD, OUT_MODE><<<(uint32_t)rows, 128, 0, a.stream>>>((const float*)a.b[0].ptr, a.b[1].ptr, n_splits, 0);
+    const cudaError_t e = launch_dependent(reduce_kernel<HD, OUT_MODE>, dim3((uint32_t)rows), dim3(128), 0, a.stream, (const float*)a.b[0].ptr,
+                                           a.b[1].ptr, n_splits, 0);
     ++*a.launches;
-    return check_cuda(a, cudaGetLastError(), "attn_reduce");
+    return check_cuda(a, e, "attn_reduce");
 }
 template int launch_reduce<256, 0>(const LaunchArgs&);
 template int launch_reduce<512, 0>(const LaunchArgs&);

@@ -208,6 +208,8 @@ __global__ void __launch_bounds__(PRE_THREADS)
                                uint32_t table_len, uint32_t page, const uint32_t* __restrict__ step, uint32_t n_kv, uint32_t half_rot,
                                size_t n_blocks, size_t dst_rows, uint32_t* status)
 {
+    pdl_wait();  // the raw q, k, v rows come from earlier kernels of the stream
+    pdl_launch_dependents();
     const size_t g = (size_t)blockIdx.x * PRE_THREADS + threadIdx.x;
     const size_t q_base = (2 * n_blocks + 31) / 32 * 32;  // the Q blocks start on a warp boundary
     if (g >= q_base) {
@@ -345,13 +347,13 @@ int launch_kv_norm_rope_append_paged_q8_d128(const LaunchArgs& a)
     const size_t n_blocks = a.b[0].bytes / 64;
     if (n_blocks == 0) return 0;
     auto kern = p.plus_one ? kv_norm_rope_append_kernel<true> : kv_norm_rope_append_kernel<false>;
-    kern<<<grid_for(2 * n_blocks), PRE_THREADS, 0, a.stream>>>(
+    const cudaError_t e = launch_dependent(kern, dim3(grid_for(2 * n_blocks)), dim3(PRE_THREADS), 0, a.stream,
         nullptr, nullptr, nullptr, 1u, (size_t)0,
         (const __half*)a.b[0].ptr, (const __half*)a.b[1].ptr, (const float*)a.b[2].ptr, (const float2*)a.b[3].ptr, (__half*)a.b[4].ptr,
         (int8_t*)a.b[5].ptr, (__half*)a.b[6].ptr, (int8_t*)a.b[7].ptr, (const uint32_t*)a.b[8].ptr, (uint32_t)(a.b[8].bytes / 4), p.page,
         (const uint32_t*)a.b[9].ptr, p.row_len / 128, p.rot_dims / 2, n_blocks, dst_rows, a.status);
     ++*a.launches;
-    return check_cuda(a, cudaGetLastError(), "kv_norm_rope_append_paged_q8_d128");
+    return check_cuda(a, e, "kv_norm_rope_append_paged_q8_d128");
 }
 
 // qkv_norm_rope_append_paged_q8_d128: q_raw f16[n x n_q x128], q_w f32[128], q_out f16, then the ten bindings of
@@ -379,13 +381,13 @@ int launch_qkv_norm_rope_append_paged_q8_d128(const LaunchArgs& a)
     if (n_blocks == 0) return 0;
     const size_t q_base = (2 * n_blocks + 31) / 32 * 32;
     auto kern = p.plus_one ? kv_norm_rope_append_kernel<true> : kv_norm_rope_append_kernel<false>;
-    kern<<<grid_for(q_base + nq_blocks), PRE_THREADS, 0, a.stream>>>(
+    const cudaError_t e = launch_dependent(kern, dim3(grid_for(q_base + nq_blocks)), dim3(PRE_THREADS), 0, a.stream,
         (const __half*)a.b[0].ptr, (const float*)a.b[1].ptr, (__half*)a.b[2].ptr, p.n_q_heads, nq_blocks, (const __half*)kv[0].ptr,
         (const __half*)kv[1].ptr, (const float*)kv[2].ptr, (const float2*)kv[3].ptr, (__half*)kv[4].ptr, (int8_t*)kv[5].ptr,
         (__half*)kv[6].ptr, (int8_t*)kv[7].ptr, (const uint32_t*)kv[8].ptr, (uint32_t)(kv[8].bytes / 4), p.page,
         (const uint32_t*)kv[9].ptr, p.row_len / 128, p.rot_dims / 2, n_blocks, dst_rows, a.status);
     ++*a.launches;
-    return check_cuda(a, cudaGetLastError(), "qkv_norm_rope_append_paged_q8_d128");
+    return check_cuda(a, e, "qkv_norm_rope_append_paged_q8_d128");
 }
 
 }  // namespace sgb

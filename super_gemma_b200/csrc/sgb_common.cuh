@@ -252,6 +252,12 @@ __device__ __forceinline__ float2 ex2_poly2(float2 x)
     return make_float2(__int_as_float(__float_as_int(p.x) + (__float_as_int(t.x) << 23)),
                        __int_as_float(__float_as_int(p.y) + (__float_as_int(t.y) << 23)));
 }
+// Programmatic dependent launch: a kernel launched with the stream-serialization attribute may start while its
+// predecessor in the stream still runs; it must call pdl_wait() before it touches anything the predecessor
+// (or anything earlier in the stream) wrote.  pdl_launch_dependents() lets the successor's CTAs be scheduled as
+// soon as every CTA of this grid has called it.  Both are no-ops for a plain launch.
+__device__ __forceinline__ void pdl_wait() { asm volatile("griddepcontrol.wait;" ::: "memory"); }
+__device__ __forceinline__ void pdl_launch_dependents() { asm volatile("griddepcontrol.launch_dependents;" ::: "memory"); }
 // Barrier `id` (1..15; 0 is __syncthreads) over `threads` threads of the CTA, a multiple of 32.
 __device__ __forceinline__ void named_barrier_sync(uint32_t id, uint32_t threads)
 {

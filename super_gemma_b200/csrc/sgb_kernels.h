@@ -49,6 +49,25 @@ int encode_tensor_map(const LaunchArgs& a, void* out_map /*CUtensorMap*/, int el
                       void* base, const uint64_t* dims, const uint64_t* strides_bytes, const uint32_t* box,
                       int swizzle /*0 none, 3 = 128B*/);
 
+// Launch `kern` so that it may overlap the tail of its predecessor in the stream (programmatic dependent
+// launch); the kernel calls pdl_wait() before reading.  SGB_PDL=0 in the environment turns the attribute off.
+bool pdl_enabled();
+template <typename... KArgs, typename... Args>
+cudaError_t launch_dependent(void (*kern)(KArgs...), dim3 grid, dim3 block, size_t smem, cudaStream_t stream, Args... args)
+{
+    cudaLaunchConfig_t cfg = {};
+    cfg.gridDim = grid;
+    cfg.blockDim = block;
+    cfg.dynamicSmemBytes = smem;
+    cfg.stream = stream;
+    cudaLaunchAttribute attr[1];
+    attr[0].id = cudaLaunchAttributeProgrammaticStreamSerialization;
+    attr[0].val.programmaticStreamSerializationAllowed = pdl_enabled() ? 1 : 0;
+    cfg.attrs = attr;
+    cfg.numAttrs = 1;
+    return cudaLaunchKernelEx(&cfg, kern, static_cast<KArgs>(args)...);
+}
+
 // The registry (sgb_registry.cu).
 const KernelEntry* registry(int* count);
 

@@ -29,6 +29,15 @@ static int set_error(int code, const std::string& msg)
 
 int set_last_error(int code, const std::string& msg) { return set_error(code, msg); }
 
+bool pdl_enabled()
+{
+    static const bool on = [] {
+        const char* e = getenv("SGB_PDL");
+        return !(e && e[0] == '0');
+    }();
+    return on;
+}
+
 int fail_validation(const LaunchArgs& a, const std::string& msg)
 {
     if (a.err) *a.err = msg;

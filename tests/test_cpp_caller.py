@@ -36,3 +36,15 @@ def test_cpp_caller_replays_the_reference_decode_test():
     _build()
     r = subprocess.run([EXE], capture_output=True, text=True)
     assert r.returncode == 0, r.stdout + r.stderr
+
+
+def test_cpp_page_cache_mirror():
+    from super_gemma_b200 import build
+
+    build.build()
+    pkg = os.path.join(ROOT, "super_gemma_b200")
+    exe = os.path.join(ROOT, "tests", "cpp", "page_cache.bin")
+    subprocess.run(["g++", "-std=c++17", "-O2", "-I", os.path.join(ROOT, "include"), os.path.join(ROOT, "tests", "cpp", "page_cache.cpp"), "-o", exe,
+                    f"-L{pkg}", "-l:libsgattn.so", f"-Wl,-rpath,{pkg}"], check=True)
+    r = subprocess.run([exe], capture_output=True, text=True)
+    assert r.returncode == 0 and "page cache ok" in r.stdout, r.stdout + r.stderr
