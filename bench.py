@@ -4,14 +4,15 @@
     python bench.py --gpus N --steps K --warmup W            # this library (CUDA, through the C ABI)
     python bench.py --impl reference --gpus N --steps K ...  # the reference's math on the host cores
 
-Headline workload (BASELINE config 5a, the 128K-context case of the metric): a 4096-token query
+Headline workload (config 5a of the benchmark definition, the 128K-context case of the metric): a 4096-token query
 chunk at q0 = 126976 attends causally to 131072 cached tokens held as Q8_0 in 256-token pages
 behind a seeded random page table; 32 query / 16 kv heads, head_dim 128.  A step is one pass:
 dequantise-and-gather K and V, then the tcgen05 flash kernel.  With N GPUs the kv heads are split
-into N groups (strong scaling, no data-path collective).  The JSON line also carries the other
-BASELINE configs under "extra": config 2 (8192 x 8192 prefill), config 3 (32K decode), config 4
-(4-token verify at 64K) and config 5b (128K decode, sequence-split over the ranks with an NCCL
-all-gather of the (acc, m, l) partials and a rank-ordered combine).
+into N groups (strong scaling, no data-path collective).  The JSON line also carries the definition's
+other configs under "extra": config 2 (8192 x 8192 prefill), config 3 (32K decode), config 4
+(4-token verify at 64K), the recorded per-token decode block, and config 5b (128K decode, sequence-split
+over the ranks; the combine and the exchange of the (acc, m, l) partials run as one kernel over peer
+memory, with the reduce + NCCL all-gather + combine form timed beside it).
 
 All inputs are synthetic: seeded N(0,1) rounded to f16, quantised on the device by this library's
 own kv_append_paged_q8_d128 (bit-exact with the oracle's quantiser, see tests/test_gpu_kv.py).

@@ -85,7 +85,7 @@ def alloc_exchange(dist, device, world: int, rank: int, rows: int):
     """Allocate the zeroed exchange buffer of this rank so that every rank of `dist`'s world can store into it,
     and return (buffer tensor, int64 tensor of all ranks' buffer addresses as seen from this GPU, keep-alive).
     Peer mappings come from torch's symmetric memory when the platform offers it, else from CUDA IPC
-    handles.  Plain peer memory only: no multicast object is asked for."""
+    handles.  Plain peer mappings only."""
     import os
 
     import torch

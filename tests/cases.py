@@ -12,7 +12,7 @@ from oracle import sg_oracle as O
 H, KV, D, G, PAGE = 32, 16, 128, 2, 256
 SCALE = 0.08838834764831845  # 1/sqrt(128)
 
-# BASELINE tolerance for attention outputs in f32: |got - want| <= 2e-3 + 1e-2 * |want|
+# Tolerance for attention outputs in f32: |got - want| <= 2e-3 + 1e-2 * |want|
 ATOL, RTOL = 2e-3, 1e-2
 
 

@@ -117,7 +117,7 @@ def test_paged_decode_small_and_ragged(ctx, kv_len, n_splits):
 
 @pytest.mark.parametrize("n_splits", [16, 32, 64])
 def test_paged_decode_32k_random_table(ctx, n_splits):
-    """BASELINE config 3: 1 query x 32768 Q8_0 tokens, 128 pages, seeded random page table."""
+    """benchmark config 3: 1 query x 32768 Q8_0 tokens, 128 pages, seeded random page table."""
     c = PagedCase(ctx, 0x5603, 32768)
     _, got = c.run(n_splits)
     assert_close(got, c.want(), what=f"cfg3 splits={n_splits}")
@@ -137,7 +137,7 @@ def test_paged_equals_linear_bit_for_bit(ctx):
 
 @pytest.mark.parametrize("kv_len,m_q,n_splits", [(7, 4, 2), (260, 2, 3), (65540, 4, 32)])
 def test_speculative_verify_is_causal_among_the_draft(ctx, kv_len, m_q, n_splits):
-    """BASELINE config 4, global part: the draft tokens are appended first, then query i sees
+    """benchmark config 4, global part: the draft tokens are appended first, then query i sees
     keys t <= kv_len - m_q + i.  There is no reference kernel for this step; the oracle is the f64
     attention at q0 = kv_len - m_q, i.e. the prefill kernels' semantics at M = m_q."""
     c = PagedCase(ctx, 0x5604, kv_len, m_q=m_q)
@@ -176,7 +176,7 @@ def test_rank_partials_combine_in_rank_order(ctx):
 
 
 def test_sliding_decode_d128(ctx):
-    """BASELINE config 4, sliding part at decode: full wrapped ring in physical order."""
+    """benchmark config 4, sliding part at decode: full wrapped ring in physical order."""
     import super_gemma_b200 as sg
 
     kv_len, n_splits = 1024, 16

@@ -117,7 +117,7 @@ def _run_linear(ctx, kernel, bufs, m, q0, n_kv, push):
 @pytest.mark.parametrize("m,q0,window", [(512, 0, 1024), (64, 0, 0), (100, 37, 0), (200, 1531, 1024), (256, 3000, 1024), (1, 5, 0),
                                          (130, 900, 1024)])
 def test_flash_f16_linear(ctx, m, q0, window):
-    """(512, 0, 1024) is BASELINE config 1: 512 queries, f16 contiguous K/V, causal with a
+    """(512, 0, 1024) is benchmark config 1: 512 queries, f16 contiguous K/V, causal with a
     1024-token window, f32 output."""
     q16, k16, v16, bufs = _linear_case(ctx, 0x5601 + m + q0, m, q0)
     want = O.attention_f64(q16.astype(np.float32), k16.astype(np.float32), v16.astype(np.float32), m, q0, H, KV, D, SCALE,
@@ -154,7 +154,7 @@ def test_flash_key_range_cut_into_pieces(ctx, monkeypatch, pieces, m, q0, window
 # ---- head_dim 128: ring history + chunk ------------------------------------------------------------------
 @pytest.mark.parametrize("q0,m", [(0, 64), (100, 64), (1000, 64), (1531, 64), (1531, 200), (66000, 4)])
 def test_sliding_ring_d128(ctx, q0, m):
-    """q0 = 1531 is the reference's wrapped-ring case; (66000, 4) is BASELINE config 4's sliding
+    """q0 = 1531 is the reference's wrapped-ring case; (66000, 4) is benchmark config 4's sliding
     part: a 4-token draft over a ring that has wrapped many times."""
     R = 1024
     rng = np.random.default_rng(0x5804 + q0 + m)
@@ -217,7 +217,7 @@ def test_paged_q8_prefill_small(ctx, m, q0, page):
 
 
 def test_paged_q8_prefill_8k_identity_table_sampled(ctx):
-    """BASELINE config 2: 8192 x 8192 causal, Q8_0 K/V in 256-token pages, identity table.  The
+    """benchmark config 2: 8192 x 8192 causal, Q8_0 K/V in 256-token pages, identity table.  The
     f64 oracle is evaluated on a seeded sample of query rows (all heads)."""
     m, q0 = 8192, 0
     q16, k, v, bufs, L = _paged_prefill(ctx, 0x5602, m, q0, identity=True)
