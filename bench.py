@@ -259,34 +259,78 @@ def run_prefill(dev, rank, world, steps, warmup, dist, m, ctx_len, identity, see
     res["sample"] = out[:: max(1, m // 7), 0, :4].float().cpu().numpy().tolist() if rank == 0 else None
 
     if e2e:
-        # The same pass through the C ABI with HOST buffers: pinned Q, K/V pools, page table and step
-        # words go up every step, the f32 output comes back every step.
-        host = {n: torch.empty(t.shape, dtype=t.dtype).pin_memory() for n, t in
-                (("q", q), ("kq", kq), ("ks", ks), ("vq", vq), ("vs", vs), ("tab", table_t))}
-        for n, t in (("q", q), ("kq", kq), ("ks", ks), ("vq", vq), ("vs", vs), ("tab", table_t)):
+        # The same pass through the C ABI with HOST buffers: pinned Q, K/V pools, page table and step words go up
+        # every step, the f32 output comes back every step.  Uploads, compute and the read-back run on three
+        # streams over two sets of device buffers, so step i + 1 is uploaded while step i computes (a server
+        # streams the next chunk's inputs the same way); events order the reuse of each set.
+        names = ("q", "kq", "ks", "vq", "vs", "tab")
+        dev_sets = [dict(zip(names, (q, kq, ks, vq, vs, table_t)))]
+        dev_sets.append({n: torch.empty_like(t) for n, t in dev_sets[0].items()})
+        outs = [out, torch.empty_like(out)]
+        host = {n: torch.empty(t.shape, dtype=t.dtype).pin_memory() for n, t in dev_sets[0].items()}
+        for n, t in dev_sets[0].items():
             host[n].copy_(t)
-        out_h = torch.empty(out.shape, dtype=out.dtype).pin_memory()
-        ups = [(b_q, host["q"]), (b_kq, host["kq"]), (b_ks, host["ks"]), (b_vq, host["vq"]), (b_vs, host["vs"]), (b_tab, host["tab"])]
+        out_h = [torch.empty(out.shape, dtype=out.dtype).pin_memory() for _ in range(2)]
+        up_stream, down_stream = torch.cuda.Stream(dev.device), torch.cuda.Stream(dev.device)
+        up_ctx = dev.sg.GpuContext(dev.device.index, stream=up_stream.cuda_stream)
+        down_ctx = dev.sg.GpuContext(dev.device.index, stream=down_stream.cuda_stream)
+        adopt = lambda c, t: c.adopt(t.data_ptr(), t.numel() * t.element_size(), np.uint8, keep=t)
+        up_bufs = [{n: adopt(up_ctx, t) for n, t in d.items()} for d in dev_sets]
+        cmp_bufs = [{n: W(t) for n, t in d.items()} for d in dev_sets]
+        cmp_out = [W(o) for o in outs]
+        down_out = [adopt(down_ctx, o) for o in outs]
         L = dev.sg.lib()
-        h2d = sum(t.numel() * t.element_size() for _, t in ups) + 16
-        d2h = out_h.numel() * 4
+        chk = dev.sg.gpu._check
+        h2d = sum(t.numel() * t.element_size() for t in host.values()) + 16
+        d2h = out.numel() * 4
+        ev = lambda: [torch.cuda.Event() for _ in range(2)]
+        uploaded, computed, downloaded = ev(), ev(), ev()
 
-        def step_e2e(timer, base):
-            if timer is not None:
-                timer.stamp(base)
-            for buf, t in ups:
-                dev.sg.gpu._check(L.sgb_buffer_upload_async(buf._h, 0, t.data_ptr(), t.numel() * t.element_size()))
+        def pipeline_step(i):
+            s_ = i % 2
+            if i >= 2:
+                up_stream.wait_event(computed[s_])        # the set's previous contents have been consumed
+            for n in names:
+                t = host[n]
+                chk(L.sgb_buffer_upload_async(up_bufs[s_][n]._h, 0, t.data_ptr(), t.numel() * t.element_size()))
+            uploaded[s_].record(up_stream)
+            dev.stream.wait_event(uploaded[s_])
+            if i >= 2:
+                dev.stream.wait_event(downloaded[s_])     # out[s_] has been read back
+            c = cmp_bufs[s_]
             dev.sg.StepState(pos=q0, kv_len_global=ctx_len, q0=q0).write_to(b_step)
-            dev.ctx.dispatch(deq, dev.bind(b_ks, b_kq, b_tab, b_kl, b_step), (row, PAGE), [1, 1, 1])
-            dev.ctx.dispatch(deq, dev.bind(b_vs, b_vq, b_tab, b_vl, b_step), (row, PAGE), [1, 1, 1])
-            dev.ctx.dispatch(flash, dev.bind(b_q, b_kl, b_vl, b_out, b_step), (SCALE, 0), [n_kv, m, 1])
-            dev.sg.gpu._check(L.sgb_buffer_download_async(b_out._h, 0, out_h.data_ptr(), d2h))
-            dev.ctx.sync()
+            dev.ctx.dispatch(deq, dev.bind(c["ks"], c["kq"], c["tab"], b_kl, b_step), (row, PAGE), [1, 1, 1])
+            dev.ctx.dispatch(deq, dev.bind(c["vs"], c["vq"], c["tab"], b_vl, b_step), (row, PAGE), [1, 1, 1])
+            dev.ctx.dispatch(flash, dev.bind(c["q"], b_kl, b_vl, cmp_out[s_], b_step), (SCALE, 0), [n_kv, m, 1])
+            computed[s_].record(dev.stream)
+            down_stream.wait_event(computed[s_])
+            chk(L.sgb_buffer_download_async(down_out[s_]._h, 0, out_h[s_].data_ptr(), d2h))
+            downloaded[s_].record(down_stream)
 
-        e_steps = max(2, min(steps, 5))
-        total_e, _, _ = timed(dev, step_e2e, e_steps, 1, dist)
+        e_steps = max(4, min(steps, 10))
+        for i in range(2):
+            pipeline_step(i)
+        torch.cuda.synchronize()
+        if dist is not None:
+            dist.barrier()
+        t0, t1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+        t0.record(dev.stream)
+        up_stream.wait_event(t0)                          # nothing of the timed steps starts before t0
+        for i in range(e_steps):
+            pipeline_step(i + 2)
+        for e in downloaded:
+            dev.stream.wait_event(e)                      # the last results are on the host before t1
+        t1.record(dev.stream)
+        torch.cuda.synchronize()
+        total_e = t0.elapsed_time(t1) * 1e-3
+        if dist is not None:
+            tt = torch.tensor([total_e], dtype=torch.float64, device=dev.device)
+            dist.all_reduce(tt, op=dist.ReduceOp.MAX)
+            total_e = float(tt.item())
+        same = bool(torch.equal(out_h[0], out_h[1])) and bool(torch.equal(out_h[0].to(dev.device), outs[0]))
         res["e2e"] = {"value": flop_total * e_steps / total_e / 1e12, "unit": "TFLOP/s", "h2d_bytes_per_step": int(h2d * world),
-                      "d2h_bytes_per_step": int(d2h * world), "ms_per_step": total_e / e_steps * 1e3}
+                      "d2h_bytes_per_step": int(d2h * world), "ms_per_step": total_e / e_steps * 1e3, "steps": e_steps,
+                      "pipelined": "uploads, compute and read-back on three streams over two buffer sets", "outputs_agree": same}
     return res
 
 
