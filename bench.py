@@ -602,21 +602,22 @@ def main():
                                                  "frac_of_burst_peak": c2["flop_total"] / (c2["flash_ms"] * 1e-3) / 1e12 / pk["tf_burst"]}
                 torch.cuda.empty_cache()
                 best = None
-                # 37 and 74 splits x 16 kv heads make 592 = 148 x 4 CTAs: every SM holds the same number
-                for ns in (32, 37, 64, 74):
+                # the library's hint (74 on 148 SMs: 16 kv heads x 74 splits x 2 warps fill every SM evenly) beside 32 / 64
+                hint = dev.ctx.decode_splits_hint(KV, 32768)
+                for ns in sorted({32, 64, hint}):
                     d3 = run_decode(dev, rank, world, 40, 5, dist, 32768, 1, ns, 0x5603)
                     if best is None or d3["kernel_us"] < best["kernel_us"]:
                         best = d3
                 best["hbm_frac_kernel"] = best["kernel_gbs"] / pk["hbm_gbs"]
                 extra["config3_decode_32k"] = best
                 torch.cuda.empty_cache()
-                d4 = run_decode(dev, rank, world, 40, 5, dist, 65536, 4, 64, 0x5604, copies=2)
+                d4 = run_decode(dev, rank, world, 40, 5, dist, 65536, 4, dev.ctx.decode_splits_hint(KV, 65536), 0x5604, copies=2)
                 d4["hbm_frac_kernel"] = d4["kernel_gbs"] / pk["hbm_gbs"]
                 extra["config4_verify_64k"] = d4
                 torch.cuda.empty_cache()
                 extra["decode_block_32k"] = run_decode_block(dev, 40, 5, 32768, 64, 0x5606)
                 torch.cuda.empty_cache()
-            d5 = run_decode(dev, rank, world, 40, 5, dist, 131072, 1, 64 if world < 4 else 32, 0x5605, copies=2)
+            d5 = run_decode(dev, rank, world, 40, 5, dist, 131072, 1, dev.ctx.decode_splits_hint(KV, 131072 // world), 0x5605, copies=2)
             d5["hbm_frac_kernel"] = d5["kernel_gbs"] / pk["hbm_gbs"]
             extra["config5b_decode_128k"] = d5
         except Exception as e:  # the headline line must still be printed

@@ -19,9 +19,12 @@
 //                        from its [key][dim] tile
 // S is double-buffered in TMEM and the three roles talk through mbarriers only, so Q K^T of the
 // next tile and P V of the previous one run while the softmax warps work.  Two CTAs fit per SM
-// (112 KB smem, 256 TMEM columns each).  Every mbarrier wait is bounded; TMEM is always freed.
+// (96 KB smem, 256 TMEM columns each).  Every mbarrier wait is bounded; TMEM is always freed.
 #include <cmath>
 #include <cstdlib>
+#include <map>
+#include <mutex>
+#include <utility>
 
 #include "sgb_common.cuh"
 #include "sgb_kernels.h"
@@ -50,14 +53,13 @@ constexpr uint32_t TMEM_S = 0;     // S: two buffers of 64 f32 columns
 constexpr uint32_t TMEM_O = 128;   // O: 128 f32 columns
 constexpr float RESCALE_T = 8.0f;
 
-// 112 KB of tiles + 128 B of barriers.  Two CTAs must fit in the SM's 228 KB next to the 1 KB the
+// 96 KB of tiles + 128 B of barriers.  Two CTAs must fit in the SM's 228 KB next to the 1 KB the
 // system reserves per CTA, so the struct is NOT padded to its 1024-byte tile alignment: the dynamic
 // shared-memory base is declared 1024-aligned instead (and checked at run time).
 struct FlashSmem {
     uint8_t q[2][2 * HALF_TILE];             // [dim half][128 rows x 128 B]
     uint8_t k[KV_STAGES][2][HALF_TILE];      // [stage][dim half][64 keys x 128 B]
     uint8_t v[KV_STAGES][2][HALF_TILE];
-    uint8_t p[2 * HALF_TILE];                // [128 rows x 128 B] = 64 f16 keys per row
     uint64_t full_k[KV_STAGES];              // TMA -> MMA warp
     uint64_t full_v[KV_STAGES];
     uint64_t s_ready[2];                     // MMA commit: S[b] holds Q K^T of a tile
@@ -70,7 +72,7 @@ struct FlashSmem {
     uint32_t abort;                          // a bounded wait ran out somewhere in the CTA
     uint32_t pad[8];
 };
-static_assert(sizeof(FlashSmem) == 7 * 2 * HALF_TILE + 128, "tiles + barriers, no padding");
+static_assert(sizeof(FlashSmem) == 6 * 2 * HALF_TILE + 128, "tiles + barriers, no padding");
 static_assert(2 * (sizeof(FlashSmem) + 1024) <= 228 * 1024, "two CTAs per SM");
 
 struct FlashParams {
@@ -448,12 +450,16 @@ __global__ void __launch_bounds__(256) combine_pieces_kernel(const float* __rest
     *reinterpret_cast<float4*>(out + (size_t)row * HD + lane * 4) = make_float4(acc.x * inv, acc.y * inv, acc.z * inv, acc.w * inv);
 }
 
-// Scratch for the pieces, one growing allocation per device, made outside stream capture only.
+// Scratch for the pieces: one growing allocation per (device, stream), made outside stream capture only.
+// Launches on one stream are ordered, so they can share a block; launches on different streams may overlap
+// and get a block each.  Blocks are never freed before the process ends: work in flight, or a recorded
+// graph, may still point at them.
 struct PieceScratch {
     float* ptr = nullptr;
     size_t bytes = 0;
 };
-PieceScratch g_piece_scratch[64];
+std::mutex g_piece_mutex;
+std::map<std::pair<int, cudaStream_t>, PieceScratch> g_piece_scratch;
 
 // How many pieces to cut every unit's key range into.  The host does not know kv_len (it lives in the
 // step buffer), so the choice rests on the grid alone: with `units` equal CTAs on `slots` resident
@@ -543,21 +549,19 @@ int run_flash(const LaunchArgs& a, const BufView& q, const BufView& k0, const Bu
     float* part_ml = nullptr;
     if (pieces > 1) {
         const size_t need = rows * pieces * (HD + 2) * sizeof(float);
-        PieceScratch& sc = g_piece_scratch[a.device < 64 ? a.device : 0];
-        if (a.device >= 64) pieces = 1;
-        if (pieces > 1 && sc.bytes < need) {
+        std::lock_guard<std::mutex> lock(g_piece_mutex);
+        PieceScratch& sc = g_piece_scratch[std::make_pair(a.device, a.stream)];
+        if (sc.bytes < need) {
             cudaStreamCaptureStatus cap = cudaStreamCaptureStatusNone;
             cudaStreamIsCapturing(a.stream, &cap);
             if (cap != cudaStreamCaptureStatusNone) {
                 pieces = 1;  // no allocation while a graph is being recorded: run whole units
             } else {
-                if (sc.ptr) {
-                    cudaDeviceSynchronize();  // an earlier launch may still read the old block
-                    cudaFree(sc.ptr);
-                    sc = PieceScratch{};
-                }
-                if (cudaMalloc(&sc.ptr, need) == cudaSuccess) {
-                    sc.bytes = need;
+                // A block that no longer suffices is kept, not freed: a recorded graph may still point at it.
+                const size_t want = need > 2 * sc.bytes ? need : 2 * sc.bytes;  // geometric growth bounds what is left behind
+                sc = PieceScratch{};
+                if (cudaMalloc(&sc.ptr, want) == cudaSuccess) {
+                    sc.bytes = want;
                 } else {
                     (void)cudaGetLastError();
                     sc = PieceScratch{};

@@ -258,6 +258,20 @@ void* sgb_ctx_stream(const sgb_ctx* c) { return c ? (void*)c->stream : nullptr; 
 int sgb_ctx_sm_count(const sgb_ctx* c) { return c ? c->sm_count : 0; }
 uint64_t sgb_launch_count(const sgb_ctx* c) { return c ? c->launches : 0; }
 
+uint32_t sgb_decode_paged_splits_hint(const sgb_ctx* c, uint32_t n_kv_heads, uint32_t kv_len)
+{
+    // attn_decode_paged_q8kv_d128 runs 4 warps per CTA and 16 warps per SM.  Two warps per (kv head, split) measured
+    // best; the hint makes n_kv_heads * n_splits * 2 warps fill every SM's 16 places exactly (148 SMs, 16 kv heads:
+    // 74), and keeps at least 256 tokens per split.
+    const uint32_t sms = c && c->sm_count > 0 ? (uint32_t)c->sm_count : 148u;
+    if (n_kv_heads == 0) return 1;
+    uint32_t n = sms * 16u / (n_kv_heads * 2u);
+    const uint32_t by_len = kv_len / 256u;
+    if (n > by_len) n = by_len;
+    if (n > 1024u) n = 1024u;
+    return n ? n : 1u;
+}
+
 int sgb_sync(sgb_ctx* c, uint32_t timeout_ms)
 {
     if (!c) return set_error(SGB_ERR_VALIDATION, "sgb_sync: ctx is NULL");

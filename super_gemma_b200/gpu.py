@@ -113,6 +113,7 @@ ABI = {
     "sgb_dispatch": (_int, [_vp, _vp, C.POINTER(_Binding), _u32, _vp, _sz, C.POINTER(_u32)]),
     "sgb_dispatch_blocking": (_int, [_vp, _vp, C.POINTER(_Binding), _u32, _vp, _sz, C.POINTER(_u32)]),
     "sgb_launch_count": (_u64, [_vp]),
+    "sgb_decode_paged_splits_hint": (_u32, [_vp, _u32, _u32]),
     "sgb_graph_begin": (_int, [_vp]),
     "sgb_graph_end": (_int, [_vp, _PP]),
     "sgb_graph_launch": (_int, [_vp, _vp]),
@@ -338,6 +339,10 @@ class GpuContext:
     @property
     def stream(self) -> int:
         return lib().sgb_ctx_stream(self._h) or 0
+
+    def decode_splits_hint(self, n_kv_heads: int, kv_len: int) -> int:
+        """A split count for the paged decode / verify kernels that fills every SM evenly."""
+        return lib().sgb_decode_paged_splits_hint(self._h, n_kv_heads, kv_len)
 
     @property
     def launch_count(self) -> int:

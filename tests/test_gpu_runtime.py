@@ -103,3 +103,14 @@ def test_buffers_are_zeroed_and_slices_share_memory(ctx):
     s.write(np.arange(256, dtype=np.float32))
     full = b.read()
     assert np.array_equal(full[256:512], np.arange(256, dtype=np.float32)) and not full[:256].any() and not full[512:].any()
+
+
+def test_decode_splits_hint_fills_the_sms():
+    import super_gemma_b200 as sg
+
+    ctx = sg.GpuContext(0)
+    sms = sg.lib().sgb_ctx_sm_count(ctx._h)
+    n = ctx.decode_splits_hint(16, 1 << 20)
+    assert n == sms * 16 // 32 and (16 * n * 2) % 4 == 0  # two warps per (kv head, split), 16 warps per SM
+    assert ctx.decode_splits_hint(16, 2048) == 8           # at least 256 tokens per split
+    assert ctx.decode_splits_hint(16, 10) == 1
