@@ -615,7 +615,7 @@ def main():
                 d4["hbm_frac_kernel"] = d4["kernel_gbs"] / pk["hbm_gbs"]
                 extra["config4_verify_64k"] = d4
                 torch.cuda.empty_cache()
-                extra["decode_block_32k"] = run_decode_block(dev, 40, 5, 32768, 64, 0x5606)
+                extra["decode_block_32k"] = run_decode_block(dev, 40, 5, 32768, dev.ctx.decode_splits_hint(KV, 32768), 0x5606)
                 torch.cuda.empty_cache()
             d5 = run_decode(dev, rank, world, 40, 5, dist, 131072, 1, dev.ctx.decode_splits_hint(KV, 131072 // world), 0x5605, copies=2)
             d5["hbm_frac_kernel"] = d5["kernel_gbs"] / pk["hbm_gbs"]
