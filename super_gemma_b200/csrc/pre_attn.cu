@@ -8,8 +8,9 @@
 //   attn_norm_rope_d128                       norm + rope of a [rows x 128] tensor in one pass
 //   kv_norm_rope_append_paged_q8_d128         norm(k) + rope(k) + norm(v) + Q8_0 quantise + paged append
 // The fused kernels round to f16 exactly where the chain stores f16 (after the norm, after the rotation), so
-// they give the bits of their own unfused pieces.  All of it is HBM-bound: 64-byte accesses, one 32-value
-// block per thread, the row's sum of squares combined with a fixed shuffle tree (deterministic).
+// they give the bits of their own unfused pieces.  All of it is HBM-bound: the head_dim-128 kernels give a row to 16
+// consecutive lanes (16-byte accesses, partner dims and block maxima by shuffle), the reference-named ones a 32-value
+// block to a thread; the row's sum of squares always goes through a fixed shuffle tree (deterministic).
 //
 // Arithmetic (f32): inv = 1/sqrt(sum(x^2)/n + 1e-6); y = f16(x * inv * w)  [w or 1 + w];
 // rope pair i couples dims (i, i + n/2), live for i < rot_dims/2: lo' = f16(lo*c - hi*s), hi' = f16(hi*c + lo*s).
@@ -121,140 +122,164 @@ __global__ void __launch_bounds__(PRE_THREADS) rope_kernel(__half* __restrict__ 
     *hi = __float2half_rn(__fadd_rn(__fmul_rn(b, cs.x), __fmul_rn(a, cs.y)));
 }
 
-// One 32-dim block of a 128-dim row after norm and rotation, as f16-exact floats.  The four threads of a row
-// are consecutive lanes; thread `sub` owns dims [32 sub, 32 sub + 32) and reads its rotation partner's block
-// (dims +-64) again from memory, which the partner thread has just pulled into L1.
+// One 8-dim piece of a 128-dim row after norm and rotation, as f16-exact floats.  The 16 threads of a row are
+// consecutive lanes (two rows per warp, 16-byte accesses); thread `o` owns dims [8 o, 8 o + 8) and gets its
+// rotation partner's normalised values (dims +-64, lane o ^ 8) by shuffle.  Every lane of the warp must call
+// it (dead lanes with live = false), and half_rot must be the same for the whole warp.
 template <bool PLUS_ONE>
-__device__ __forceinline__ void norm_rope_block_d128(const __half* __restrict__ row_ptr, const float* __restrict__ w,
-                                                      const float2* __restrict__ cs_row, uint32_t half_rot, int sub, bool live,
-                                                      float (&own)[32])
+__device__ __forceinline__ void norm_rope_oct_d128(const __half* __restrict__ row_ptr, const float* __restrict__ w,
+                                                    const float2* __restrict__ cs_row, uint32_t half_rot, int o, bool live,
+                                                    float (&v)[8])
 {
-    float other[32];
     if (live) {
-        load_f16x32(row_ptr + sub * 32, own);
+        const uint4 u = __ldg(reinterpret_cast<const uint4*>(row_ptr + 8 * o));
+        const __half2* h = reinterpret_cast<const __half2*>(&u);
+#pragma unroll
+        for (int j = 0; j < 4; j++) {
+            const float2 f = __half22float2(h[j]);
+            v[2 * j] = f.x;
+            v[2 * j + 1] = f.y;
+        }
     } else {
 #pragma unroll
-        for (int i = 0; i < 32; i++) own[i] = 0.0f;
+        for (int i = 0; i < 8; i++) v[i] = 0.0f;
     }
-    const float inv = row_inv_rms<4>(own);
-    if (!live) return;
-    const int psub = sub ^ 2;
-    const bool rotates = half_rot > (uint32_t)((sub & 1) * 32);  // any live pair among this block's 32
-    if (rotates) load_f16x32(row_ptr + psub * 32, other);
-    apply_norm<PLUS_ONE>(own, inv, w ? w + sub * 32 : nullptr);
-    if (!rotates) return;
-    apply_norm<PLUS_ONE>(other, inv, w ? w + psub * 32 : nullptr);
+    float ss = 0.0f;
 #pragma unroll
-    for (int i = 0; i < 32; i++) {
-        const uint32_t pair = (uint32_t)((sub & 1) * 32 + i);
-        if (pair < half_rot) {
-            const float2 cs = __ldg(cs_row + pair);
+    for (int i = 0; i < 8; i++) ss = fmaf(v[i], v[i], ss);
+#pragma unroll
+    for (int d = 1; d < 16; d <<= 1) ss += __shfl_xor_sync(0xffffffffu, ss, d);  // fixed tree: every lane gets the same bits
+    const float inv = rsqrtf(ss / 128.0f + RMS_EPS);
+    float wv[8];
+#pragma unroll
+    for (int i = 0; i < 8; i++) wv[i] = 1.0f;
+    if (w != nullptr && live) {
+        const float4 w0 = __ldg(reinterpret_cast<const float4*>(w + 8 * o)), w1 = __ldg(reinterpret_cast<const float4*>(w + 8 * o) + 1);
+        const float t[8] = {w0.x, w0.y, w0.z, w0.w, w1.x, w1.y, w1.z, w1.w};
+#pragma unroll
+        for (int i = 0; i < 8; i++) wv[i] = PLUS_ONE ? 1.0f + t[i] : t[i];
+    }
+#pragma unroll
+    for (int i = 0; i < 8; i++) v[i] = round_f16(v[i] * inv * wv[i]);
+    if (half_rot == 0) return;
+    float other[8];
+#pragma unroll
+    for (int i = 0; i < 8; i++) other[i] = __shfl_xor_sync(0xffffffffu, v[i], 8);
+    const uint32_t pair0 = (uint32_t)(o & 7) * 8;
+    if (!live || pair0 >= half_rot) return;
+    const float4* cp = reinterpret_cast<const float4*>(cs_row + pair0);  // (cos, sin) pairs; 16-byte aligned: half_rot % 8 == 0
+#pragma unroll
+    for (int j = 0; j < 4; j++) {  // half_rot is a multiple of 8 (checked on the host): all 8 pairs of a live piece rotate
+        const float4 cs = __ldg(cp + j);
+        const float c[2] = {cs.x, cs.z}, sn[2] = {cs.y, cs.w};
+#pragma unroll
+        for (int e = 0; e < 2; e++) {
+            const int i = 2 * j + e;
             // low half: lo*c - hi*s with lo = own; high half: hi*c + lo*s with hi = own
-            own[i] = (sub < 2) ? round_f16(__fsub_rn(__fmul_rn(own[i], cs.x), __fmul_rn(other[i], cs.y)))
-                               : round_f16(__fadd_rn(__fmul_rn(own[i], cs.x), __fmul_rn(other[i], cs.y)));
+            v[i] = (o < 8) ? round_f16(__fsub_rn(__fmul_rn(v[i], c[e]), __fmul_rn(other[i], sn[e])))
+                           : round_f16(__fadd_rn(__fmul_rn(v[i], c[e]), __fmul_rn(other[i], sn[e])));
         }
     }
+}
+
+__device__ __forceinline__ uint4 pack_f16x8(const float (&v)[8])
+{
+    uint32_t w[4];
+#pragma unroll
+    for (int j = 0; j < 4; j++) {
+        const __half2 h = __floats2half2_rn(v[2 * j], v[2 * j + 1]);
+        w[j] = *reinterpret_cast<const uint32_t*>(&h);
+    }
+    return make_uint4(w[0], w[1], w[2], w[3]);
 }
 
 // attn_norm_rope_d128: x f16[rows x 128] (rows = tokens x n_heads), w f32[128], cos_sin f32[tokens x rot/2 x 2], y f16.
 template <bool PLUS_ONE>
 __global__ void __launch_bounds__(PRE_THREADS) norm_rope_d128_kernel(const __half* __restrict__ x, const float* __restrict__ w,
                                                                      const float2* __restrict__ cos_sin, __half* __restrict__ y,
-                                                                     uint32_t n_heads, uint32_t half_rot, size_t n_blocks)
+                                                                     uint32_t n_heads, uint32_t half_rot, uint32_t rows)
 {
-    const size_t blk = (size_t)blockIdx.x * PRE_THREADS + threadIdx.x;
-    const bool live = blk < n_blocks;
-    const size_t row = blk / 4;
-    const int sub = (int)(blk % 4);
-    float v[32];
-    norm_rope_block_d128<PLUS_ONE>(x + row * 128, w, cos_sin + (row / n_heads) * half_rot, half_rot, sub, live, v);
-    if (!live) return;
-    uint4 out[4];
-    pack_f16x32(v, out);
-    uint4* o = reinterpret_cast<uint4*>(y + blk * 32);
-#pragma unroll
-    for (int i = 0; i < 4; i++) o[i] = out[i];
+    // 32-bit index arithmetic (the host checks rows * 16 < 2^32): 64-bit divisions would cost more than the rest
+    const uint32_t g = blockIdx.x * PRE_THREADS + threadIdx.x;
+    const uint32_t row = g >> 4;
+    const int o = (int)(g & 15);
+    const bool live = row < rows;
+    float v[8];
+    norm_rope_oct_d128<PLUS_ONE>(x + (size_t)row * 128, w, cos_sin + (size_t)(row / n_heads) * half_rot, half_rot, o, live, v);
+    if (live) *reinterpret_cast<uint4*>(y + (size_t)row * 128 + 8 * o) = pack_f16x8(v);
 }
 
-// Q8_0 of one block of f16-exact values: the arithmetic of kv_quant_q8.wgsl:38-57 (see kv_codec.cu).
-__device__ __forceinline__ void quant_block_f32(const float (&x)[32], __half& scale, uint32_t (&packed)[8])
+// Q8_0 of the 32-value block that four consecutive lanes hold (8 values each): the arithmetic of
+// kv_quant_q8.wgsl:38-57 (see kv_codec.cu); the block maximum by two shuffles.  All lanes of the warp call it.
+__device__ __forceinline__ void quant_oct_f32(const float (&x)[8], __half& scale, uint2& packed)
 {
     float amax = 0.0f;
 #pragma unroll
-    for (int i = 0; i < 32; i++) amax = fmaxf(amax, fabsf(x[i]));
+    for (int i = 0; i < 8; i++) amax = fmaxf(amax, fabsf(x[i]));
+    amax = fmaxf(amax, __shfl_xor_sync(0xffffffffu, amax, 1));
+    amax = fmaxf(amax, __shfl_xor_sync(0xffffffffu, amax, 2));
     const float d = __fmul_rn(amax, 1.0f / 127.0f);
     const float id = d > 0.0f ? __fdiv_rn(1.0f, d) : 0.0f;
     scale = __float2half_rn(d);
+    uint32_t p[2] = {0u, 0u};
 #pragma unroll
-    for (int w = 0; w < 8; w++) {
-        uint32_t p = 0;
-#pragma unroll
-        for (int b = 0; b < 4; b++) p |= (uint32_t)(__float2int_rn(__fmul_rn(x[w * 4 + b], id)) & 0xFF) << (8 * b);
-        packed[w] = p;
-    }
+    for (int i = 0; i < 8; i++) p[i >> 2] |= (uint32_t)(__float2int_rn(__fmul_rn(x[i], id)) & 0xFF) << (8 * (i & 3));
+    packed = make_uint2(p[0], p[1]);
 }
 
-// kv_norm_rope_append_paged_q8_d128: blocks [0, n) are K (norm with k_w, rope), blocks [n, 2n) are V (weightless
-// norm); each lands Q8_0-quantised at row page_table[t / page] * page + t % page, t = step[0] + token.
-// qkv_norm_rope_append_paged_q8_d128 adds nq blocks for Q after them, from the next warp boundary on (norm with
-// q_w, rope, f16 out): the whole pre-attention step of a layer in one launch.
+// kv_norm_rope_append_paged_q8_d128: three warp-aligned segments of 16 threads per row: K rows (norm with k_w, rope),
+// V rows (weightless norm), both landing Q8_0-quantised at row page_table[t / page] * page + t % page with
+// t = step[0] + token; and, for qkv_norm_rope_append_paged_q8_d128, Q rows (norm with q_w, rope, f16 out): the
+// whole pre-attention step of a layer in one launch.
 template <bool PLUS_ONE>
 __global__ void __launch_bounds__(PRE_THREADS)
     kv_norm_rope_append_kernel(const __half* __restrict__ q_raw, const float* __restrict__ q_w, __half* __restrict__ q_out,
-                               uint32_t n_q, size_t nq_blocks,
+                               uint32_t n_q, uint32_t q_rows,
                                const __half* __restrict__ k_raw, const __half* __restrict__ v_raw, const float* __restrict__ k_w,
                                const float2* __restrict__ cos_sin, __half* __restrict__ k_scales, int8_t* __restrict__ k_quants,
                                __half* __restrict__ v_scales, int8_t* __restrict__ v_quants, const uint32_t* __restrict__ page_table,
                                uint32_t table_len, uint32_t page, const uint32_t* __restrict__ step, uint32_t n_kv, uint32_t half_rot,
-                               size_t n_blocks, size_t dst_rows, uint32_t* status)
+                               uint32_t kv_rows, size_t dst_rows, uint32_t* status)
 {
     pdl_wait();  // the raw q, k, v rows come from earlier kernels of the stream
     pdl_launch_dependents();
-    const size_t g = (size_t)blockIdx.x * PRE_THREADS + threadIdx.x;
-    const size_t q_base = (2 * n_blocks + 31) / 32 * 32;  // the Q blocks start on a warp boundary
-    if (g >= q_base) {
-        const size_t blk = g - q_base;
-        const bool q_live = blk < nq_blocks;
-        const size_t row = blk / 4;
-        float v[32];
-        norm_rope_block_d128<PLUS_ONE>(q_raw + row * 128, q_w, cos_sin + (row / n_q) * half_rot, half_rot, (int)(blk % 4), q_live, v);
-        if (!q_live) return;
-        uint4 out[4];
-        pack_f16x32(v, out);
-        uint4* o = reinterpret_cast<uint4*>(q_out + blk * 32);
-#pragma unroll
-        for (int i = 0; i < 4; i++) o[i] = out[i];
+    // 32-bit index arithmetic (the host checks the thread count < 2^32): 64-bit divisions would cost more than the rest
+    const uint32_t g = blockIdx.x * PRE_THREADS + threadIdx.x;
+    const uint32_t seg = (kv_rows * 16 + 31) / 32 * 32;  // threads per K or V segment: whole warps
+    float v[8];
+    if (g >= 2 * seg) {
+        const uint32_t row = (g - 2 * seg) >> 4;
+        const int o = (int)(g & 15);
+        const bool live = row < q_rows;
+        norm_rope_oct_d128<PLUS_ONE>(q_raw + (size_t)row * 128, q_w, cos_sin + (size_t)(row / n_q) * half_rot, half_rot, o, live, v);
+        if (live) *reinterpret_cast<uint4*>(q_out + (size_t)row * 128 + 8 * o) = pack_f16x8(v);
         return;
     }
-    const bool live = g < 2 * n_blocks;  // n_blocks is a multiple of 4: K and V never share a row's four lanes
-    const bool is_v = g >= n_blocks;
-    const size_t blk = is_v ? g - n_blocks : g;
-    const size_t row = blk / 4;  // (token, kv head)
-    const int sub = (int)(blk % 4);
-    const size_t token = row / n_kv;
-    float v[32];
-    norm_rope_block_d128<PLUS_ONE>((is_v ? v_raw : k_raw) + row * 128, is_v ? nullptr : k_w, cos_sin + token * half_rot,
-                                   is_v ? 0u : half_rot, sub, live, v);
+    const bool is_v = g >= seg;
+    const uint32_t row = (is_v ? g - seg : g) >> 4;  // (token, kv head)
+    const int o = (int)(g & 15);
+    const bool live = row < kv_rows;
+    const uint32_t token = row / n_kv, head = row - token * n_kv;
+    norm_rope_oct_d128<PLUS_ONE>((is_v ? v_raw : k_raw) + (size_t)row * 128, is_v ? nullptr : k_w, cos_sin + (size_t)token * half_rot,
+                                 is_v ? 0u : half_rot, o, live, v);
+    __half s;
+    uint2 packed;
+    quant_oct_f32(v, s, packed);
     if (!live) return;
-    const size_t t = (size_t)step[STEP_POS] + token;
-    const size_t p = t / page;
+    const uint32_t t = __ldg(step + STEP_POS) + token;
+    const uint32_t p = t / page;
     if (p >= table_len) {
-        report_error(status, DEV_ERR_BOUNDS, 104, (uint32_t)p, table_len);
+        report_error(status, DEV_ERR_BOUNDS, 104, p, table_len);
         return;
     }
-    const size_t dst_row = (size_t)page_table[p] * page + t % page;
+    const size_t dst_row = (size_t)__ldg(page_table + p) * page + (t - p * page);
     if (dst_row >= dst_rows) {
         report_error(status, DEV_ERR_BOUNDS, 105, (uint32_t)dst_row, (uint32_t)dst_rows);
         return;
     }
-    __half s;
-    uint32_t packed[8];
-    quant_block_f32(v, s, packed);
-    const size_t dblk = (dst_row * n_kv + row % n_kv) * 4 + sub;
-    (is_v ? v_scales : k_scales)[dblk] = s;
-    uint4* o = reinterpret_cast<uint4*>((is_v ? v_quants : k_quants) + dblk * 32);
-    o[0] = make_uint4(packed[0], packed[1], packed[2], packed[3]);
-    o[1] = make_uint4(packed[4], packed[5], packed[6], packed[7]);
+    const size_t drow = dst_row * n_kv + head;  // row of [128] quants / [4] scales
+    if ((o & 3) == 0) (is_v ? v_scales : k_scales)[drow * 4 + (o >> 2)] = s;
+    *reinterpret_cast<uint2*>((is_v ? v_quants : k_quants) + drow * 128 + 8 * o) = packed;
 }
 
 inline uint32_t grid_for(size_t n) { return (uint32_t)((n + PRE_THREADS - 1) / PRE_THREADS); }
@@ -312,17 +337,18 @@ template int launch_rope<512, 128, 4>(const LaunchArgs&);
 int launch_norm_rope_d128(const LaunchArgs& a)
 {
     const PushNormRope p = *(const PushNormRope*)a.push;
-    if (p.n_heads == 0 || p.rot_dims > 128 || p.rot_dims % 2) return fail_validation(a, "attn_norm_rope_d128: n_heads > 0, even rot_dims <= 128");
+    if (p.n_heads == 0 || p.rot_dims > 128 || p.rot_dims % 16) return fail_validation(a, "attn_norm_rope_d128: n_heads > 0, rot_dims a multiple of 16 up to 128");
     if (a.b[0].bytes % (256 * (size_t)p.n_heads)) return fail_validation(a, "attn_norm_rope_d128: x is not whole tokens of n_heads x 128");
     const size_t rows = a.b[0].bytes / 256;
     if (int r = need_bytes(a, 1, 128 * 4, "w")) return r;
     if (int r = need_bytes(a, 2, rows / p.n_heads * (p.rot_dims / 2) * 8, "cos_sin")) return r;
     if (int r = need_bytes(a, 3, a.b[0].bytes, "y")) return r;
-    const size_t n_blocks = rows * 4;
-    if (n_blocks == 0) return 0;
+    if (rows == 0) return 0;
+    if (rows >= (1u << 27)) return fail_validation(a, "attn_norm_rope_d128: at most 2^27 rows per launch");
+    if (reinterpret_cast<uintptr_t>(a.b[2].ptr) & 15) return fail_validation(a, "attn_norm_rope_d128: cos_sin must be 16-byte aligned");
     auto kern = p.plus_one ? norm_rope_d128_kernel<true> : norm_rope_d128_kernel<false>;
-    kern<<<grid_for(n_blocks), PRE_THREADS, 0, a.stream>>>((const __half*)a.b[0].ptr, (const float*)a.b[1].ptr, (const float2*)a.b[2].ptr,
-                                                          (__half*)a.b[3].ptr, p.n_heads, p.rot_dims / 2, n_blocks);
+    kern<<<grid_for(rows * 16), PRE_THREADS, 0, a.stream>>>((const __half*)a.b[0].ptr, (const float*)a.b[1].ptr, (const float2*)a.b[2].ptr,
+                                                           (__half*)a.b[3].ptr, p.n_heads, p.rot_dims / 2, (uint32_t)rows);
     ++*a.launches;
     return check_cuda(a, cudaGetLastError(), "attn_norm_rope_d128");
 }
@@ -332,8 +358,8 @@ int launch_norm_rope_d128(const LaunchArgs& a)
 int launch_kv_norm_rope_append_paged_q8_d128(const LaunchArgs& a)
 {
     const PushKvNormRope p = *(const PushKvNormRope*)a.push;
-    if (p.row_len == 0 || p.row_len % 128 || p.page == 0 || p.rot_dims > 128 || p.rot_dims % 2)
-        return fail_validation(a, "kv_norm_rope_append_paged_q8_d128: row_len = n_kv_heads*128, page > 0, even rot_dims <= 128");
+    if (p.row_len == 0 || p.row_len % 128 || p.page == 0 || p.rot_dims > 128 || p.rot_dims % 16)
+        return fail_validation(a, "kv_norm_rope_append_paged_q8_d128: row_len = n_kv_heads*128, page > 0, rot_dims a multiple of 16 up to 128");
     if (a.b[0].bytes % (p.row_len * 2) || a.b[1].bytes != a.b[0].bytes)
         return fail_validation(a, "kv_norm_rope_append_paged_q8_d128: k_raw and v_raw must be the same whole rows");
     const size_t tokens = a.b[0].bytes / (p.row_len * 2);
@@ -344,14 +370,17 @@ int launch_kv_norm_rope_append_paged_q8_d128(const LaunchArgs& a)
     if (a.b[7].bytes / p.row_len != dst_rows) return fail_validation(a, "kv_norm_rope_append_paged_q8_d128: K and V pools differ in rows");
     if (a.b[4].bytes / 2 < dst_rows * (p.row_len / 32) || a.b[6].bytes / 2 < dst_rows * (p.row_len / 32))
         return fail_validation(a, "kv_norm_rope_append_paged_q8_d128: scales buffer too short for the quants buffer");
-    const size_t n_blocks = a.b[0].bytes / 64;
-    if (n_blocks == 0) return 0;
+    const size_t kv_rows = a.b[0].bytes / 256;
+    if (kv_rows == 0) return 0;
+    if (kv_rows >= (1u << 26)) return fail_validation(a, "kv_norm_rope_append_paged_q8_d128: at most 2^26 (token, head) rows per launch");
+    if (reinterpret_cast<uintptr_t>(a.b[3].ptr) & 15) return fail_validation(a, "kv_norm_rope_append_paged_q8_d128: cos_sin must be 16-byte aligned");
+    const size_t seg = (kv_rows * 16 + 31) / 32 * 32;
     auto kern = p.plus_one ? kv_norm_rope_append_kernel<true> : kv_norm_rope_append_kernel<false>;
-    const cudaError_t e = launch_dependent(kern, dim3(grid_for(2 * n_blocks)), dim3(PRE_THREADS), 0, a.stream,
-        nullptr, nullptr, nullptr, 1u, (size_t)0,
+    const cudaError_t e = launch_dependent(kern, dim3(grid_for(2 * seg)), dim3(PRE_THREADS), 0, a.stream,
+        nullptr, nullptr, nullptr, 1u, 0u,
         (const __half*)a.b[0].ptr, (const __half*)a.b[1].ptr, (const float*)a.b[2].ptr, (const float2*)a.b[3].ptr, (__half*)a.b[4].ptr,
         (int8_t*)a.b[5].ptr, (__half*)a.b[6].ptr, (int8_t*)a.b[7].ptr, (const uint32_t*)a.b[8].ptr, (uint32_t)(a.b[8].bytes / 4), p.page,
-        (const uint32_t*)a.b[9].ptr, p.row_len / 128, p.rot_dims / 2, n_blocks, dst_rows, a.status);
+        (const uint32_t*)a.b[9].ptr, p.row_len / 128, p.rot_dims / 2, (uint32_t)kv_rows, dst_rows, a.status);
     ++*a.launches;
     return check_cuda(a, e, "kv_norm_rope_append_paged_q8_d128");
 }
@@ -361,8 +390,8 @@ int launch_kv_norm_rope_append_paged_q8_d128(const LaunchArgs& a)
 int launch_qkv_norm_rope_append_paged_q8_d128(const LaunchArgs& a)
 {
     const PushQkvNormRope p = *(const PushQkvNormRope*)a.push;
-    if (p.n_q_heads == 0 || p.row_len == 0 || p.row_len % 128 || p.page == 0 || p.rot_dims > 128 || p.rot_dims % 2)
-        return fail_validation(a, "qkv_norm_rope_append_paged_q8_d128: n_q_heads > 0, row_len = n_kv_heads*128, page > 0, even rot_dims <= 128");
+    if (p.n_q_heads == 0 || p.row_len == 0 || p.row_len % 128 || p.page == 0 || p.rot_dims > 128 || p.rot_dims % 16)
+        return fail_validation(a, "qkv_norm_rope_append_paged_q8_d128: n_q_heads > 0, row_len = n_kv_heads*128, page > 0, rot_dims a multiple of 16 up to 128");
     const BufView* kv = a.b + 3;
     if (kv[0].bytes % (p.row_len * 2) || kv[1].bytes != kv[0].bytes)
         return fail_validation(a, "qkv_norm_rope_append_paged_q8_d128: k_raw and v_raw must be the same whole rows");
@@ -377,15 +406,18 @@ int launch_qkv_norm_rope_append_paged_q8_d128(const LaunchArgs& a)
     if (kv[7].bytes / p.row_len != dst_rows) return fail_validation(a, "qkv_norm_rope_append_paged_q8_d128: K and V pools differ in rows");
     if (kv[4].bytes / 2 < dst_rows * (p.row_len / 32) || kv[6].bytes / 2 < dst_rows * (p.row_len / 32))
         return fail_validation(a, "qkv_norm_rope_append_paged_q8_d128: scales buffer too short for the quants buffer");
-    const size_t n_blocks = kv[0].bytes / 64, nq_blocks = a.b[0].bytes / 64;
-    if (n_blocks == 0) return 0;
-    const size_t q_base = (2 * n_blocks + 31) / 32 * 32;
+    const size_t kv_rows = kv[0].bytes / 256, q_rows = a.b[0].bytes / 256;
+    if (kv_rows == 0) return 0;
+    if (kv_rows >= (1u << 26) || q_rows >= (1u << 26))
+        return fail_validation(a, "qkv_norm_rope_append_paged_q8_d128: at most 2^26 (token, head) rows of q and of k per launch");
+    if (reinterpret_cast<uintptr_t>(kv[3].ptr) & 15) return fail_validation(a, "qkv_norm_rope_append_paged_q8_d128: cos_sin must be 16-byte aligned");
+    const size_t seg = (kv_rows * 16 + 31) / 32 * 32;
     auto kern = p.plus_one ? kv_norm_rope_append_kernel<true> : kv_norm_rope_append_kernel<false>;
-    const cudaError_t e = launch_dependent(kern, dim3(grid_for(q_base + nq_blocks)), dim3(PRE_THREADS), 0, a.stream,
-        (const __half*)a.b[0].ptr, (const float*)a.b[1].ptr, (__half*)a.b[2].ptr, p.n_q_heads, nq_blocks, (const __half*)kv[0].ptr,
+    const cudaError_t e = launch_dependent(kern, dim3(grid_for(2 * seg + q_rows * 16)), dim3(PRE_THREADS), 0, a.stream,
+        (const __half*)a.b[0].ptr, (const float*)a.b[1].ptr, (__half*)a.b[2].ptr, p.n_q_heads, (uint32_t)q_rows, (const __half*)kv[0].ptr,
         (const __half*)kv[1].ptr, (const float*)kv[2].ptr, (const float2*)kv[3].ptr, (__half*)kv[4].ptr, (int8_t*)kv[5].ptr,
         (__half*)kv[6].ptr, (int8_t*)kv[7].ptr, (const uint32_t*)kv[8].ptr, (uint32_t)(kv[8].bytes / 4), p.page,
-        (const uint32_t*)kv[9].ptr, p.row_len / 128, p.rot_dims / 2, n_blocks, dst_rows, a.status);
+        (const uint32_t*)kv[9].ptr, p.row_len / 128, p.rot_dims / 2, (uint32_t)kv_rows, dst_rows, a.status);
     ++*a.launches;
     return check_cuda(a, e, "qkv_norm_rope_append_paged_q8_d128");
 }

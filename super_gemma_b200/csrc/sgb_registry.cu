@@ -128,7 +128,7 @@ const KernelEntry REGISTRY[] = {
      "merges the local splits, stores the row into every rank's buffer over NVLink, waits (bounded) for all ranks' rows, merges in rank order",
      launch_reduce_exchange_d128},
     {"attn_norm_rope_d128", {256, 1, 1}, 4, 12,
-     "x f16[token x n_heads x128], w f32[128], cos_sin f32[token x rot/2 x2], y f16 | push {n_heads u32, rot_dims u32, plus_one u32} | "
+     "x f16[token x n_heads x128], w f32[128], cos_sin f32[token x rot/2 x2], y f16 | push {n_heads u32, rot_dims u32 (multiple of 16), plus_one u32} | "
      "RMS norm per head, then rotate-half RoPE of the first rot_dims/2 pairs (i, i+64); rounds to f16 after each, like the two-kernel chain",
      launch_norm_rope_d128},
     {"kv_norm_rope_append_paged_q8_d128", {256, 1, 1}, 10, 16,
