@@ -99,3 +99,12 @@ def test_two_rank_protocols_match_the_single_rank_oracle(tmp_path):
     full = O.attention_f64(qp.astype(np.float32), k.astype(np.float32), v.astype(np.float32), m, q0, H, KV, D, SCALE)
     got = np.concatenate([np.load(tmp_path / f"prefill_{r}.npy") for r in range(world)], axis=1)
     assert np.array_equal(got, full)
+
+
+def test_exchange_buffer_layout():
+    """Words of one rank's exchange buffer for attn_reduce_exchange_d128: two parities of world x rows merged rows
+    of 130 floats, their flags, and one epoch per row."""
+    from super_gemma_b200 import sharding
+
+    assert sharding.exchange_words(1, 32) == 2 * 32 * 130 + 2 * 32 + 32
+    assert sharding.exchange_words(8, 128) == 2 * 8 * 128 * 130 + 2 * 8 * 128 + 128
