@@ -63,3 +63,29 @@ def test_two_ranks_match_the_nccl_path():
            "--master-port", "29533", os.path.join(ROOT, "tests", "exchange_worker.py")]
     r = subprocess.run(cmd, capture_output=True, text=True, timeout=300, cwd=ROOT)
     assert r.returncode == 0 and "exchange worker: OK" in r.stdout, r.stdout[-2000:] + r.stderr[-2000:]
+
+
+def test_absent_peer_ends_in_a_timeout_status_not_a_hang():
+    """The wait for a peer's row is bounded (about a second): with a second rank that never stores its row the kernel
+    gives up, reports DEV_ERR_TIMEOUT through the status word, writes NaN (never stale data), and the context stays
+    usable.  The absent peer is a second local buffer that nothing writes; no GPU is faulted or hung."""
+    import super_gemma_b200 as sg
+    from super_gemma_b200 import sharding
+
+    ctx = sg.GpuContext(0)
+    rows, n_splits = 4, 2
+    mine = ctx.new_buffer(sharding.exchange_words(2, rows), np.float32)
+    absent = ctx.new_buffer(sharding.exchange_words(2, rows), np.float32)
+    peers = ctx.buffer_from_iter(np.array([mine.device_ptr, absent.device_ptr], np.uint64))
+    part = np.random.default_rng(3).standard_normal((rows, n_splits, D + 2)).astype(np.float32)
+    part[:, :, D + 1] = 1.0
+    out = ctx.new_buffer(rows * D, np.float32)
+    fused = ctx.load_kernel("attn_reduce_exchange_d128")
+    with pytest.raises(sg.Timeout):
+        ctx.dispatch_blocking(fused, bind(ctx.buffer_from_iter(part.reshape(-1)), mine, peers, out), (n_splits, 2, 0), [rows, 1, 1])
+    assert np.all(np.isnan(out.read()))
+    # the context is still good: the single-rank form runs right after
+    solo = ctx.new_buffer(sharding.exchange_words(1, rows), np.float32)
+    solo_peers = ctx.buffer_from_iter(np.array([solo.device_ptr], np.uint64))
+    ctx.dispatch_blocking(fused, bind(ctx.buffer_from_iter(part.reshape(-1)), solo, solo_peers, out), (n_splits, 1, 0), [rows, 1, 1])
+    assert np.all(np.isfinite(out.read()))

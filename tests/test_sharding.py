@@ -101,6 +101,45 @@ def test_two_rank_protocols_match_the_single_rank_oracle(tmp_path):
     assert np.array_equal(got, full)
 
 
+def _absent_rank_main(rank, world, port, out_dir):
+    import datetime
+    import time
+
+    import torch
+    import torch.distributed as dist
+
+    os.environ["MASTER_ADDR"], os.environ["MASTER_PORT"] = "127.0.0.1", str(port)
+    dist.init_process_group("gloo", rank=rank, world_size=world, timeout=datetime.timedelta(seconds=4))
+    dist.barrier()  # both ranks are up
+    if rank == 1:
+        time.sleep(12)  # this rank never brings its partial: a stalled or lost process
+        os._exit(0)
+    mine = torch.zeros(4)
+    t0 = time.time()
+    outcome = "completed"
+    try:
+        dist.all_gather([torch.empty_like(mine) for _ in range(world)], mine)
+    except Exception as e:  # the process-group timeout ends the collective with an error on the host
+        outcome = "error: " + type(e).__name__
+    with open(os.path.join(out_dir, "outcome.txt"), "w") as f:
+        f.write(f"{outcome}\n{time.time() - t0:.1f}\n")
+    os._exit(0)
+
+
+def test_absent_rank_is_detected_on_the_host(tmp_path):
+    """Failure detection without touching a GPU: a rank that never joins the exchange makes the other rank's
+    collective end with an error after the process-group timeout, on the host, instead of waiting for ever."""
+    import torch.multiprocessing as mp
+
+    with socket.socket() as s:
+        s.bind(("127.0.0.1", 0))
+        port = s.getsockname()[1]
+    mp.spawn(_absent_rank_main, args=(2, port, str(tmp_path)), nprocs=2, join=True)
+    outcome, seconds = (tmp_path / "outcome.txt").read_text().split()[0:1], (tmp_path / "outcome.txt").read_text().strip().split("\n")[-1]
+    assert outcome[0].startswith("error"), outcome
+    assert float(seconds) < 11.0
+
+
 def test_exchange_buffer_layout():
     """Words of one rank's exchange buffer for attn_reduce_exchange_d128: two parities of world x rows merged rows
     of 130 floats, their flags, and one epoch per row."""
