@@ -176,6 +176,34 @@ def fisher_yates(seed, n):
     return np.random.default_rng(seed).permutation(n).astype(np.uint32)
 
 
+def check_prefill_rows(dev, out, q, kq, ks, vq, vs, table, m, q0, ctx_len, local_kv, tokens):
+    """After the timed region: sampled rows of the prefill output against the f64 oracle (test infrastructure,
+    used here only as the checker).  For each of the given LOCAL kv heads the head's Q8_0 rows are brought to the
+    host, put into logical order through the page table, dequantised to f16(scale * q) by the oracle's codec and
+    attended to in f64.  Returns {"rows", "max_abs_err", "ok"}; tolerance 2e-3 + 1e-2 * |want|."""
+    from oracle import sg_oracle as O
+
+    torch = dev.torch
+    n_kv = kq.numel() // (int(table.size) * PAGE * D)
+    t = np.arange(ctx_len)
+    phys = torch.from_numpy(table.astype(np.int64)[t // PAGE] * PAGE + t % PAGE).to(dev.device)
+    worst, bad, rows = 0.0, 0, 0
+    for j in local_kv:
+        def head(quants, scales):
+            qh = quants.view(-1, n_kv, D)[:, j][phys].contiguous().cpu().numpy()
+            sh = scales.view(-1, n_kv, D // 32)[:, j][phys].contiguous().cpu().numpy().view(np.uint16)
+            return O.f16_bits_to_f32(O.dequant_q8_0_f16(sh, qh)).reshape(ctx_len, 1, D)
+        k32, v32 = head(kq, ks), head(vq, vs)
+        q32 = q[:, j * G:(j + 1) * G].float().cpu().numpy()
+        want = O.attention_f64(q32, k32, v32, m, q0, G, 1, D, SCALE, tokens=np.asarray(tokens, np.uint32))
+        got = out[:, j * G:(j + 1) * G][torch.as_tensor(np.asarray(tokens, np.int64), device=dev.device)].cpu().numpy()
+        err = np.abs(got.astype(np.float64) - want)
+        worst = max(worst, float(err.max()))
+        bad += int(np.sum((err > 2e-3 + 1e-2 * np.abs(want)) | ~np.isfinite(got)))
+        rows += got.shape[0] * got.shape[1]
+    return {"rows": rows, "max_abs_err": worst, "ok": bad == 0, "against": "f64 oracle on f16(scale*q) K/V, 2e-3 + 1e-2*|want|"}
+
+
 def timed(dev, fn, steps, warmup, dist=None, stamps_per_step=1, graph=False):
     """W untimed steps, then K steps bracketed by barrier + synchronize; returns (max-over-ranks
     seconds for the K steps, per-step stamp deltas in ns as array [K, stamps_per_step]).
@@ -220,7 +248,7 @@ def timed(dev, fn, steps, warmup, dist=None, stamps_per_step=1, graph=False):
 # --------------------------------------------------------------------------------------------------
 # workloads
 # --------------------------------------------------------------------------------------------------
-def run_prefill(dev, rank, world, steps, warmup, dist, m, ctx_len, identity, seed, e2e=False, stamps=True):
+def run_prefill(dev, rank, world, steps, warmup, dist, m, ctx_len, identity, seed, e2e=False, check=True):
     """Chunked prefill of m tokens at q0 = ctx_len - m over a ctx_len-token paged Q8_0 cache;
     kv heads split over the ranks.  Returns a dict of measurements."""
     torch = dev.torch
@@ -256,7 +284,10 @@ def run_prefill(dev, rank, world, steps, warmup, dist, m, ctx_len, identity, see
     res = {"ms_per_step": total_s / steps * 1e3, "tflops": flop_total * steps / total_s / 1e12, "launches": launches,
            "flash_ms": float(np.mean(deltas[:, 1])) * 1e-6, "dequant_ms": float(np.mean(deltas[:, 0])) * 1e-6,
            "flop_per_rank": flop_total / world, "flop_total": flop_total}
-    res["sample"] = out[:: max(1, m // 7), 0, :4].float().cpu().numpy().tolist() if rank == 0 else None
+    if check and rank == 0:
+        # run by the caller after the timed and clock-sampled region: it is CPU work
+        tokens = sorted({0, 1, 63, 64, m // 2, m - 65, m - 64, m - 1} & set(range(m)))
+        res["_check"] = lambda: check_prefill_rows(dev, out, q, kq, ks, vq, vs, table, m, q0, ctx_len, sorted({0, n_kv - 1}), tokens)
 
     if e2e:
         # The same pass through the C ABI with HOST buffers: pinned Q, K/V pools, page table and step words go up
@@ -334,6 +365,39 @@ def run_prefill(dev, rank, world, steps, warmup, dist, m, ctx_len, identity, see
     return res
 
 
+def prefill_output(dev, kvh, m, ctx_len, seed):
+    """One untimed pass of the paged prefill over the given GLOBAL kv heads; returns the output tensor [m, 2*len(kvh), D]."""
+    torch = dev.torch
+    q0, n_kv, n_pages = ctx_len - m, len(kvh), ctx_len // PAGE
+    kq, ks, vq, vs, table_t = build_paged_kv(dev, seed, ctx_len, kvh, fisher_yates(seed + 0x100, n_pages), n_pages)
+    q = build_q(dev, seed, m, [h * G + g for h in kvh for g in range(G)])
+    k_lin = torch.zeros(ctx_len * n_kv * D, dtype=torch.float16, device=dev.device)
+    v_lin = torch.zeros_like(k_lin)
+    out = torch.zeros(m, n_kv * G, D, dtype=torch.float32, device=dev.device)
+    step_t = torch.tensor([q0, 0, ctx_len, q0], dtype=torch.int32, device=dev.device)
+    torch.cuda.synchronize()
+    W = dev.wrap
+    dev.ctx.dispatch_blocking(dev.kernel("attn_prefill_paged_q8kv_flash_d128"),
+                              dev.bind(*map(W, (q, kq, ks, vq, vs, table_t, k_lin, v_lin, out, step_t))), (SCALE, PAGE), [n_kv, m, 1])
+    return out
+
+
+def check_sharded_prefill(dev, rank, world, dist, m=512, ctx_len=8192, seed=0x5607):
+    """Every rank computes its kv-head slice the way the sharded run does, and the same heads inside a launch over
+    all 16 kv heads the way a 1-GPU run does; the two must agree (the launch geometry may cut the key range into a
+    different number of pieces, so agreement is to rounding, not to the bit)."""
+    torch = dev.torch
+    mine = list(range(rank * KV // world, (rank + 1) * KV // world))
+    a = prefill_output(dev, mine, m, ctx_len, seed)
+    b = prefill_output(dev, list(range(KV)), m, ctx_len, seed)[:, mine[0] * G:(mine[-1] + 1) * G]
+    diff = float((a - b).abs().max().item())
+    ok = torch.tensor([1 if (diff <= 2e-5 and bool(torch.isfinite(a).all())) else 0], device=dev.device)
+    worst = torch.tensor([diff], dtype=torch.float64, device=dev.device)
+    dist.all_reduce(ok, op=dist.ReduceOp.MIN)
+    dist.all_reduce(worst, op=dist.ReduceOp.MAX)
+    return {"agrees": bool(ok.item() == 1), "max_abs_diff": float(worst.item()), "shape": f"{m} queries over {ctx_len} tokens, every rank"}
+
+
 def run_decode(dev, rank, world, steps, warmup, dist, ctx_len, m_q, n_splits, seed, copies=4):
     """Decode (m_q = 1) or verify (m_q = 4) over a ctx_len-token paged Q8_0 cache.  With world > 1
     the sequence is split into contiguous page ranges; each rank merges its own splits to
@@ -361,22 +425,30 @@ def run_decode(dev, rank, world, steps, warmup, dist, ctx_len, m_q, n_splits, se
     dec = dev.kernel("attn_decode_paged_q8kv_d128" if m_q == 1 else "attn_verify_paged_q8kv_d128")
     red, redp, comb = dev.kernel("attn_reduce_f32_d128"), dev.kernel("attn_reduce_partial_d128"), dev.kernel("attn_combine_ranks_d128")
 
-    def step(timer, base):
-        kq, ks, vq, vs, tab = b_pools[base % len(b_pools)]
-        if timer is not None:
-            timer.stamp(base)
-        dev.ctx.dispatch(dec, dev.bind(b_q, kq, ks, vq, vs, tab, b_part, b_step), (n_splits, SCALE, PAGE), [KV, n_splits, m_q])
-        if timer is not None:
-            timer.stamp(base + 1)
-        if world == 1:
-            dev.ctx.dispatch(red, dev.bind(b_part, b_out), n_splits, [rows, 1, 1])
-        else:
-            dev.ctx.dispatch(redp, dev.bind(b_part, b_mine), n_splits, [rows, 1, 1])
-            with torch.cuda.stream(dev.stream):
-                dist.all_gather_into_tensor(gathered, mine)
-            dev.ctx.dispatch(comb, dev.bind(b_gath, b_out), world, [rows, 1, 1])
+    def make_step(mid_stamp, tail):
+        def step(timer, base):
+            kq, ks, vq, vs, tab = b_pools[base % len(b_pools)]
+            if timer is not None:
+                timer.stamp(base)
+            dev.ctx.dispatch(dec, dev.bind(b_q, kq, ks, vq, vs, tab, b_part, b_step), (n_splits, SCALE, PAGE), [KV, n_splits, m_q])
+            if timer is not None and mid_stamp:
+                timer.stamp(base + 1)
+            tail()
+        return step
 
-    total_s, deltas, launches = timed(dev, step, steps, warmup, dist, stamps_per_step=2, graph=(world == 1))
+    def tail_local():
+        dev.ctx.dispatch(red, dev.bind(b_part, b_out), n_splits, [rows, 1, 1])
+
+    def tail_nccl():
+        dev.ctx.dispatch(redp, dev.bind(b_part, b_mine), n_splits, [rows, 1, 1])
+        with torch.cuda.stream(dev.stream):
+            dist.all_gather_into_tensor(gathered, mine)
+        dev.ctx.dispatch(comb, dev.bind(b_gath, b_out), world, [rows, 1, 1])
+
+    tail0 = tail_local if world == 1 else tail_nccl
+    # the decode kernel alone (a stamp between the two kernels), then the whole step with nothing between them
+    _, deltas, _ = timed(dev, make_step(True, tail0), steps, warmup, dist, stamps_per_step=2, graph=(world == 1))
+    total_s, _, launches = timed(dev, make_step(False, tail0), steps, warmup, dist, stamps_per_step=1, graph=(world == 1))
     kv_bytes = ctx_len * KV * (D + 8) * 2  # quants + scales, K and V
     algo = kv_bytes + m_q * H * D * 2 + m_q * H * D * 4 + (ctx_len // PAGE) * 4
     kern_us = float(np.median(deltas[:, 0])) * 1e-3
@@ -390,21 +462,47 @@ def run_decode(dev, rank, world, steps, warmup, dist, ctx_len, m_q, n_splits, se
 
             xbuf, peers, keep = sharding.alloc_exchange(dist, dev.device, world, rank, rows)
             b_x, b_peers = W(xbuf), W(peers)
-            fx = dev.kernel("attn_reduce_exchange_d128")
+            fx, fxt = dev.kernel("attn_reduce_exchange_d128"), dev.kernel("attn_reduce_exchange_timed_d128")
 
-            def step_fused(timer, base):
-                kq, ks, vq, vs, tab = b_pools[base % len(b_pools)]
-                if timer is not None:
-                    timer.stamp(base)
-                dev.ctx.dispatch(dec, dev.bind(b_q, kq, ks, vq, vs, tab, b_part, b_step), (n_splits, SCALE, PAGE), [KV, n_splits, m_q])
-                if timer is not None:
-                    timer.stamp(base + 1)
-                dev.ctx.dispatch(fx, dev.bind(b_part, b_x, b_peers, b_out), (n_splits, world, rank), [rows, 1, 1])
+            def tail_fused():
+                dev.ctx.dispatch(fx, dev.bind(b_part, b_x, b_peers, b_out), (n_splits, world, rank, 0), [rows, 1, 1])
 
-            total_f, _, launches_f = timed(dev, step_fused, steps, warmup, dist, stamps_per_step=2, graph=True)
+            total_f, _, launches_f = timed(dev, make_step(False, tail_fused), steps, warmup, dist, stamps_per_step=1, graph=True)
             res.update({"nccl_us_per_step": res["us_per_step"], "nccl_gbs": res["gbs"], "us_per_step": total_f / steps * 1e6,
                         "gbs": algo * steps / total_f / 1e9, "launches": launches_f,
                         "exchange": f"one kernel, peer stores over NVLink ({keep[1]}); nccl_* = reduce + all-gather + combine"})
+            # Correctness of what was just timed: the same pool through both arms, compared bit for bit on every rank.
+            make_step(False, tail_nccl)(None, 0)
+            dev.ctx.sync()
+            out_nccl = out.clone()
+            out.zero_()
+            make_step(False, tail_fused)(None, 0)
+            dev.ctx.sync()
+            same = bool(torch.equal(out_nccl.view(torch.int32), out.view(torch.int32))) and bool(torch.isfinite(out).all())
+            flag = torch.tensor([1 if same else 0], device=dev.device)
+            dist.all_reduce(flag, op=dist.ReduceOp.MIN)
+            res["exchange_agrees"] = bool(flag.item() == 1)
+            # Where the exchange kernel's time goes: global-timer stamps at its four phase boundaries, per row.
+            stamps = torch.zeros(rows * 5, dtype=torch.int64, device=dev.device)
+            b_st = W(stamps)
+            phases = []
+            tail_timed = lambda: dev.ctx.dispatch(fxt, dev.bind(b_part, b_x, b_peers, b_out, b_st), (n_splits, world, rank, 0), [rows, 1, 1])
+            step_timed = make_step(False, tail_timed)
+            # eight steps replayed as one graph keep the ranks in step with one another (through the exchange itself);
+            # the stamps that survive a replay are those of its last step
+            g8 = dev.ctx.record_graph(lambda _c: [step_timed(None, i) for i in range(8)])
+            for i in range(12):
+                dist.barrier()
+                dev.ctx.submit_blocking(g8)
+                if i >= 2:
+                    phases.append(np.diff(stamps.cpu().numpy().reshape(rows, 5), axis=1))
+            ph = np.stack(phases).astype(np.float64) * 1e-3  # [launch, row, phase] in us
+            med = np.median(ph, axis=(0, 1))
+            wait_max = torch.tensor([float(np.median(ph[:, :, 2].max(axis=1)))], dtype=torch.float64, device=dev.device)
+            dist.all_reduce(wait_max, op=dist.ReduceOp.MAX)
+            res["exchange_phases_us"] = {"local_merge": med[0], "peer_stores_and_flags": med[1], "wait": med[2], "rank_merge": med[3],
+                                         "wait_max_over_rows_and_ranks": float(wait_max.item()),
+                                         "note": "rank 0's medians over rows and replays, last of eight graph-replayed steps"}
         except Exception as e:
             res["fused_exchange_error"] = repr(e)
     return res
@@ -561,6 +659,7 @@ def main():
     ap.add_argument("--ctx", type=int, default=131072)
     ap.add_argument("--no-extra", action="store_true", help="headline workload only")
     ap.add_argument("--no-cpu", action="store_true", help="skip the CPU baseline leg")
+    ap.add_argument("--no-e2e", action="store_true", help="skip the end-to-end (host buffers) leg")
     args = ap.parse_args()
     args.warmup = max(args.warmup, 3) if args.impl == "b200" else args.warmup
 
@@ -589,17 +688,28 @@ def main():
     dev = Dev(local_rank)  # raises without the CUDA library or a B200: there is no fallback
     pk = peaks()
     with ClockSampler(local_rank) as clocks:
-        head = run_prefill(dev, rank, world, args.steps, args.warmup, dist, args.m, args.ctx, False, SEED, e2e=True)
+        head = run_prefill(dev, rank, world, args.steps, args.warmup, dist, args.m, args.ctx, False, SEED, e2e=not args.no_e2e)
     clk = clocks.summary()
+    check = head.pop("_check", None)
+    parity = check() if check else None
+    del check
     torch.cuda.empty_cache()
 
     extra = {}
+    if world > 1:
+        try:
+            extra["sharded_prefill_check"] = check_sharded_prefill(dev, rank, world, dist)
+        except Exception as e:
+            extra["sharded_prefill_check"] = {"error": repr(e)}
+        torch.cuda.empty_cache()
     if not args.no_extra:
         try:
             if world == 1:
                 c2 = run_prefill(dev, rank, world, max(3, args.steps), 3, dist, 8192, 8192, True, 0x5602)
                 extra["config2_prefill_8192"] = {"tflops": c2["tflops"], "ms_per_step": c2["ms_per_step"], "flash_ms": c2["flash_ms"],
-                                                 "frac_of_burst_peak": c2["flop_total"] / (c2["flash_ms"] * 1e-3) / 1e12 / pk["tf_burst"]}
+                                                 "frac_of_burst_peak": c2["flop_total"] / (c2["flash_ms"] * 1e-3) / 1e12 / pk["tf_burst"],
+                                                 "parity_sample": c2.pop("_check")()}
+                del c2
                 torch.cuda.empty_cache()
                 best = None
                 # the library's hint (74 on 148 SMs: 16 kv heads x 74 splits x 2 warps fill every SM evenly) beside 32 / 64
@@ -644,7 +754,7 @@ def main():
                          "peak_kind": f"{pk['kind']} bf16 {'sustained' if long_run else 'burst'}",
                          "traffic": FLASH_DRAM_BYTES.get((args.m, args.ctx, world)),
                          "ms_per_launch": head["flash_ms"], "dequant_ms_per_step": head["dequant_ms"]},
-            "cpu_baseline": cpu, "e2e": head.get("e2e"), "gpu_launches": int(head["launches"]), "clocks": clk, "extra": extra,
+            "parity_sample": parity, "cpu_baseline": cpu, "e2e": head.get("e2e"), "gpu_launches": int(head["launches"]), "clocks": clk, "extra": extra,
         }
         print(json.dumps(line), flush=True)
     if dist is not None:

@@ -178,7 +178,13 @@ int sgb_cache2_stats(const sgb_cache2 *c, sgb_cache2_stats_t *out);
  * requests are rejected with SGB_ERR_VALIDATION.  All arguments are device pointers owned by the
  * caller; the call is asynchronous on `stream` (NULL = the legacy default stream).
  * The first call on each device resolves the static array's address and sets a kernel attribute:
- * make that first call outside any stream capture.  Every call shares the one array and leaves its
+ * make that first call outside any stream capture.  That first call is also where the CUDA runtime
+ * loads the library's device code on that device (module loading is lazy), and loading is when the
+ * driver sets the static array's 1.04 MB aside: a host that is about to commit every remaining byte
+ * of HBM must make one call per device BEFORE it does so; later calls leave free device memory
+ * unchanged.  The set-up is serialised by a lock, so first calls may come from several threads.
+ * kv_len counts the m_q query tokens themselves (append, then attend): kv_len < m_q is rejected.
+ * Every call shares the one array and leaves its
  * last partials there (each call overwrites all rows it reads, nothing needs zeroing); two calls
  * that overlap on the GPU -- different streams, or different threads -- race on it. */
 int sgb_decode_paged_q8kv_d128_noalloc(int device, void *stream, const void *q, const void *k_quants, const void *k_scales,

@@ -11,7 +11,7 @@ HERE = os.path.dirname(os.path.abspath(__file__))
 CSRC = os.path.join(HERE, "csrc")
 OUT = os.path.join(HERE, "libsgattn.so")
 SOURCES = ["sgb_runtime.cu", "sgb_registry.cu", "kv_codec.cu", "attn_generic.cu", "attn_decode_paged.cu",
-           "attn_prefill_flash.cu", "pre_attn.cu", "attn_exchange.cu", "cache2.cu"]
+           "attn_prefill_flash.cu", "pre_attn.cu", "attn_exchange.cu", "cache2.cu", "mma_probe.cu"]
 NVCC_FLAGS = ["-gencode", "arch=compute_100a,code=sm_100a", "-lineinfo", "-O3", "-std=c++17", "--use_fast_math=false",
               "-Xcompiler", "-fPIC"]
 

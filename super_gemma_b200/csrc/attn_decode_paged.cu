@@ -31,8 +31,10 @@
 #include <cstdio>
 #include <cstdlib>
 #include <initializer_list>
+#include <mutex>
 #include <string>
 
+#include "attn_merge.cuh"
 #include "sgb_common.cuh"
 #include "sgb_kernels.h"
 
@@ -489,12 +491,16 @@ cudaError_t launch_decode_variant(cudaStream_t stream, int device, const CUtenso
 {
     using Smem = DecodeSmem<NSTAGES>;
     const size_t smem = sizeof(Smem) + 1024;
+    static std::mutex attr_mutex;
     static bool attr_set[64] = {};
-    if (device >= 0 && device < 64 && !attr_set[device]) {
-        cudaError_t e = cudaFuncSetAttribute(decode_paged_kernel<NSTAGES, MIN_CTAS, SUB>,
-                                             cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
-        if (e != cudaSuccess) return e;
-        attr_set[device] = true;
+    {
+        std::lock_guard<std::mutex> lock(attr_mutex);
+        if (device >= 0 && device < 64 && !attr_set[device]) {
+            cudaError_t e = cudaFuncSetAttribute(decode_paged_kernel<NSTAGES, MIN_CTAS, SUB>,
+                                                 cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
+            if (e != cudaSuccess) return e;
+            attr_set[device] = true;
+        }
     }
     const uint32_t ctas_x = (n_kv * SUB + WPC - 1) / WPC;
     return launch_dependent(decode_paged_kernel<NSTAGES, MIN_CTAS, SUB>, dim3(ctas_x, n_splits), dim3(WPC * 32), smem, stream, tm[0], tm[1],
@@ -592,6 +598,7 @@ static __device__ __align__(256) float g_noalloc_scratch[NOALLOC_PART_FLOATS + 6
 // cudaGetSymbolAddress, once per device.
 void* g_noalloc_dev_ptr[64] = {};
 bool g_noalloc_ready[64] = {};
+std::mutex g_noalloc_mutex;  // the per-device set-up may be reached from several host threads
 
 __global__ void noalloc_step_kernel(uint32_t kv_len)
 {
@@ -602,23 +609,16 @@ __global__ void noalloc_step_kernel(uint32_t kv_len)
     step[STEP_Q0] = 0;
 }
 
-// Combine of the splits in ascending order (the arithmetic of attn_reduce.wgsl:29-56), reading the
-// partials straight from the static array.  One block per query row, one thread per dim.
-__global__ void __launch_bounds__(HD) noalloc_reduce_kernel(float* __restrict__ out, uint32_t n_splits)
+// Combine of the splits: the shared statement of attn_reduce.wgsl:29-56 (merge_splits_running, the arithmetic
+// of attn_reduce_f32_d128, so both decode entries give the same bits), reading the partials straight from the
+// static array.  One block per query row, two dims per thread.
+__global__ void __launch_bounds__(HD / 2) noalloc_reduce_kernel(float* __restrict__ out, uint32_t n_splits)
 {
     const size_t row = blockIdx.x;
-    const int d = threadIdx.x;
-    float m = NEG_SENTINEL, l = 0.0f, acc = 0.0f;
-    for (uint32_t s = 0; s < n_splits; s++) {
-        const float* p = g_noalloc_scratch + (row * n_splits + s) * (HD + 2);
-        const float ms = p[HD], ls = p[HD + 1];
-        const float m_new = fmaxf(m, ms);
-        const float ca = __expf(m - m_new), cb = __expf(ms - m_new);
-        acc = acc * ca + p[d] * cb;
-        l = l * ca + ls * cb;
-        m = m_new;
-    }
-    out[row * HD + d] = acc / l;
+    const int d0 = 2 * threadIdx.x;
+    float acc[2];
+    const MergeState st = merge_splits_running<HD, 2>(g_noalloc_scratch + row * n_splits * (HD + 2), HD + 2, n_splits, d0, acc);
+    *reinterpret_cast<float2*>(out + row * HD + d0) = make_float2(acc[0] / st.l, acc[1] / st.l);
 }
 
 }  // namespace
@@ -637,6 +637,7 @@ extern "C" int sgb_decode_paged_q8kv_d128_noalloc(int device, void* stream, cons
     if (n_kv_heads == 0 || (n_kv_heads & 1)) return set_last_error(3, "decode_noalloc: n_kv_heads must be even and > 0");
     if (m_q == 0 || m_q > 4) return set_last_error(3, "decode_noalloc: m_q must be 1..4");
     if (kv_len == 0 || n_splits == 0) return set_last_error(3, "decode_noalloc: kv_len and n_splits must be > 0");
+    if (kv_len < m_q) return set_last_error(3, "decode_noalloc: kv_len counts the m_q query tokens, so it cannot be smaller than m_q");
     if (page < (uint32_t)STAGE_TOK || (page & (page - 1)))
         return set_last_error(3, "decode_noalloc: page must be a power of two, at least 16 tokens");
     const uint64_t part_rows = (uint64_t)m_q * n_kv_heads * G * n_splits;
@@ -667,7 +668,10 @@ extern "C" int sgb_decode_paged_q8kv_d128_noalloc(int device, void* stream, cons
 
     // Set-up on the first call per device, with that device current: resolve the device address of
     // the static array (the decode launcher raises its kernel's shared-memory limit on its own first
-    // use per device).  Neither allocates.
+    // use per device).  Neither call allocates by itself, but this is where the CUDA runtime loads the
+    // module that holds the array on this device (module loading is lazy), and that is when the driver
+    // sets the array's 1.04 MB aside: the first call per device must come while that much is still free.
+    std::lock_guard<std::mutex> lock(g_noalloc_mutex);
     if (!g_noalloc_ready[device]) {
         void* ptr = nullptr;
         e = cudaGetSymbolAddress(&ptr, g_noalloc_scratch);
@@ -693,7 +697,7 @@ extern "C" int sgb_decode_paged_q8kv_d128_noalloc(int device, void* stream, cons
     e = launch_decode(s, device, sm_count, tm, (const __half*)q, page_table, table_len, page, (uint32_t)(pool_rows / page), scratch, step,
                       n_kv_heads, n_splits, scale, m_q, status);
     if (e != cudaSuccess) return set_last_error(4, std::string("decode_noalloc: launch: ") + cudaGetErrorString(e));
-    noalloc_reduce_kernel<<<m_q * n_kv_heads * G, HD, 0, s>>>(out, n_splits);
+    noalloc_reduce_kernel<<<m_q * n_kv_heads * G, HD / 2, 0, s>>>(out, n_splits);
     e = cudaGetLastError();
     if (e != cudaSuccess) return set_last_error(4, std::string("decode_noalloc: launch: ") + cudaGetErrorString(e));
     return 0;

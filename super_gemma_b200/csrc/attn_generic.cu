@@ -3,6 +3,7 @@
 // 512-token sliding prefill).  They follow the reference's streaming-softmax statement per key
 // (attn_decode_sliding.wgsl:84-107 and its siblings) with f32 math, one warp per key and the four
 // warps of a block merged in a fixed order, so reruns are bit-identical.
+#include "attn_merge.cuh"
 #include "sgb_common.cuh"
 #include "sgb_kernels.h"
 
@@ -13,7 +14,10 @@ namespace {
 constexpr int GEN_THREADS = 128;
 constexpr int GEN_WARPS = GEN_THREADS / 32;
 
-enum : int { FMT_F16 = 0, FMT_Q8 = 1 };
+// FMT_Q8: value = f32(scale) * f32(q), unrounded (attn_decode_global_q8k.wgsl:82, and the exact product the
+// int8 path of attn_prefill_global_flash_sp_iq.wgsl forms).  FMT_Q8_F16: the same product rounded to f16,
+// the value attn_prefill_global_flash_sp_q8.wgsl:104 stages in shared memory (= kv_dequant_q8).
+enum : int { FMT_F16 = 0, FMT_Q8 = 1, FMT_Q8_F16 = 2 };
 
 struct KvOperand {
     const void* data;           // f16 rows, or int8 quants
@@ -81,6 +85,10 @@ __device__ __forceinline__ void load_row(const KvOperand& op, size_t row, int kv
     } else {
         load_q8<DPL>(reinterpret_cast<const int8_t*>(op.data) + base + d0, op.scales + (row * n_kv + kvh) * (HD / 32), d0,
                      out);
+        if constexpr (FMT == FMT_Q8_F16) {
+#pragma unroll
+            for (int d = 0; d < DPL; d++) out[d] = __half2float(__float2half_rn(out[d]));
+        }
     }
 }
 
@@ -229,90 +237,32 @@ __global__ void __launch_bounds__(GEN_THREADS) decode_generic_kernel(const __hal
     }
 }
 
-// Split-K combine (attn_reduce.wgsl:29-56).  Grid = rows, 128 threads.  The reference walks the
-// splits in ascending order rescaling as it goes; that chain of dependent loads costs a DRAM
-// latency per split, so here the same sum is formed in two steps with no dependence between
-// loads: M = max_s m_s, then acc = sum_s exp(m_s - M) * acc_s and l = sum_s exp(m_s - M) * l_s,
-// both summed in ascending split order (fixed order => bit-identical reruns).
+// Split-K combine (attn_reduce.wgsl:29-56): the splits of a row in ascending order with a running
+// maximum, the reference's own op order (merge_splits_running).  Grid = rows, HD / 2 threads, two dims each.
 // OUT_MODE 0: f16(acc/l) (the reference), 1: f32 acc/l, 2: merged (acc, m, l) as f32[HD+2].
 // split_major = 0: part[(row*n + s)*(HD+2)]; 1: part[(s*rows + row)*(HD+2)] (per-rank blocks).
 constexpr int REDUCE_MAX_SPLITS = 1024;
 
 template <int HD, int OUT_MODE>
-__global__ void __launch_bounds__(128) reduce_kernel(const float* __restrict__ part, void* __restrict__ out, uint32_t n_splits,
-                                                    int split_major)
+__global__ void __launch_bounds__(HD / 2) reduce_kernel(const float* __restrict__ part, void* __restrict__ out, uint32_t n_splits,
+                                                       int split_major)
 {
-    constexpr int DPT = HD / 128;
-    __shared__ float w_s[REDUCE_MAX_SPLITS];
-    __shared__ float wl_s[REDUCE_MAX_SPLITS];
-    __shared__ float red[4];
     const size_t row = blockIdx.x, rows = gridDim.x;
-    const int t = threadIdx.x;
+    const int d0 = 2 * threadIdx.x;
     pdl_wait();  // the partials come from the kernel before this one
     pdl_launch_dependents();
     const size_t s_stride = split_major ? rows * (HD + 2) : (size_t)(HD + 2);
     const float* base = part + (split_major ? row : row * n_splits) * (HD + 2);
-
-    float mx = NEG_SENTINEL;
-    for (uint32_t s = t; s < n_splits; s += 128) {
-        const float ms = base[s * s_stride + HD];
-        w_s[s] = ms;
-        wl_s[s] = base[s * s_stride + HD + 1];
-        mx = fmaxf(mx, ms);
-    }
-#pragma unroll
-    for (int o = 16; o > 0; o >>= 1) mx = fmaxf(mx, __shfl_xor_sync(0xffffffffu, mx, o));
-    if ((t & 31) == 0) red[t >> 5] = mx;
-    __syncthreads();
-    const float m_all = fmaxf(fmaxf(red[0], red[1]), fmaxf(red[2], red[3]));
-    for (uint32_t s = t; s < n_splits; s += 128) {
-        const float w = __expf(w_s[s] - m_all);  // empty split: exp(-3e38 - m) = 0
-        w_s[s] = w;
-        wl_s[s] *= w;
-    }
-    __syncthreads();
-
-    float acc[DPT], l = 0.0f;
-#pragma unroll
-    for (int d = 0; d < DPT; d++) acc[d] = 0.0f;
-    uint32_t s = 0;
-    for (; s + 8 <= n_splits; s += 8) {
-        float v[8][DPT];
-#pragma unroll
-        for (int u = 0; u < 8; u++) {
-#pragma unroll
-            for (int d = 0; d < DPT; d++) v[u][d] = base[(s + u) * s_stride + t + 128 * d];
-        }
-#pragma unroll
-        for (int u = 0; u < 8; u++) {
-#pragma unroll
-            for (int d = 0; d < DPT; d++) acc[d] = fmaf(w_s[s + u], v[u][d], acc[d]);
-            l += wl_s[s + u];
-        }
-    }
-    for (; s < n_splits; s++) {
-#pragma unroll
-        for (int d = 0; d < DPT; d++) acc[d] = fmaf(w_s[s], base[s * s_stride + t + 128 * d], acc[d]);
-        l += wl_s[s];
-    }
-
+    float acc[2];
+    const MergeState st = merge_splits_running<HD, 2>(base, s_stride, n_splits, d0, acc);
     if constexpr (OUT_MODE == 2) {
         float* o = reinterpret_cast<float*>(out) + row * (HD + 2);
-#pragma unroll
-        for (int d = 0; d < DPT; d++) o[t + 128 * d] = acc[d];
-        if (t == 0) {
-            o[HD] = m_all;
-            o[HD + 1] = l;
-        }
+        *reinterpret_cast<float2*>(o + d0) = make_float2(acc[0], acc[1]);
+        if (threadIdx.x == 0) *reinterpret_cast<float2*>(o + HD) = make_float2(st.m, st.l);
+    } else if constexpr (OUT_MODE == 0) {
+        reinterpret_cast<__half2*>(out)[(row * HD + d0) / 2] = __floats2half2_rn(acc[0] / st.l, acc[1] / st.l);
     } else {
-#pragma unroll
-        for (int d = 0; d < DPT; d++) {
-            const float y = acc[d] / l;
-            if constexpr (OUT_MODE == 0)
-                reinterpret_cast<__half*>(out)[row * HD + t + 128 * d] = __float2half_rn(y);
-            else
-                reinterpret_cast<float*>(out)[row * HD + t + 128 * d] = y;
-        }
+        *reinterpret_cast<float2*>(reinterpret_cast<float*>(out) + row * HD + d0) = make_float2(acc[0] / st.l, acc[1] / st.l);
     }
 }
 
@@ -320,12 +270,14 @@ __global__ void __launch_bounds__(128) reduce_kernel(const float* __restrict__ p
 // from `hist` at row t % ring, then chunk rows [max(q0, t_begin) - q0, i] from `chunk`
 // (attn_prefill_sliding_ring.wgsl:88-140); otherwise one linear range [t_begin, qpos] from `hist`
 // (attn_prefill_sliding.wgsl:53-57,78 / attn_prefill_global.wgsl:53,74).  window 0 = none.
-template <int HD, int G, int KFMT, int VFMT, int TWO_RANGE, int OUT_F32>
-__global__ void __launch_bounds__(GEN_THREADS) prefill_generic_kernel(const __half* __restrict__ q, KvOperand k_hist,
-                                                                      KvOperand v_hist, KvOperand k_chunk, KvOperand v_chunk,
-                                                                      void* __restrict__ out, const uint32_t* __restrict__ step,
-                                                                      uint32_t window, uint32_t ring, float scale,
-                                                                      uint32_t* status)
+// QFMT = FMT_Q8: q holds int8 quants [M x H x HD] with f16 scales q_scales [M x H x HD/32]
+// (attn_prefill_global_flash_sp_iq.wgsl:24-25).
+template <int HD, int G, int KFMT, int VFMT, int TWO_RANGE, int OUT_F32, int QFMT = FMT_F16>
+__global__ void __launch_bounds__(GEN_THREADS) prefill_generic_kernel(const void* __restrict__ q, const __half* __restrict__ q_scales,
+                                                                      KvOperand k_hist, KvOperand v_hist, KvOperand k_chunk,
+                                                                      KvOperand v_chunk, void* __restrict__ out,
+                                                                      const uint32_t* __restrict__ step, uint32_t window,
+                                                                      uint32_t ring, float scale, uint32_t* status)
 {
     constexpr int DPL = HD / 32;
     __shared__ float sm_acc[G * HD];
@@ -341,7 +293,13 @@ __global__ void __launch_bounds__(GEN_THREADS) prefill_generic_kernel(const __ha
 
     float qr[G][DPL];
 #pragma unroll
-    for (int g = 0; g < G; g++) load_f16<DPL>(q + ((size_t)i * n_q + kvh * G + g) * HD + d0, qr[g]);
+    for (int g = 0; g < G; g++) {
+        const size_t qrow = (size_t)i * n_q + kvh * G + g;
+        if constexpr (QFMT == FMT_F16)
+            load_f16<DPL>(reinterpret_cast<const __half*>(q) + qrow * HD + d0, qr[g]);
+        else
+            load_q8<DPL>(reinterpret_cast<const int8_t*>(q) + qrow * HD + d0, q_scales + qrow * (HD / 32), d0, qr[g]);
+    }
 
     Stream<G, DPL> st;
     st.init();
@@ -488,7 +446,7 @@ int launch_reduce(const LaunchArgs& a)
     if (int r = need_bytes(a, 0, rows * n_splits * (HD + 2) * 4, "part")) return r;
     const size_t out_bytes = OUT_MODE == 0 ? rows * HD * 2 : OUT_MODE == 1 ? rows * HD * 4 : rows * (HD + 2) * 4;
     if (int r = need_bytes(a, 1, out_bytes, "out")) return r;
-    const cudaError_t e = launch_dependent(reduce_kernel<HD, OUT_MODE>, dim3((uint32_t)rows), dim3(128), 0, a.stream, (const float*)a.b[0].ptr,
+    const cudaError_t e = launch_dependent(reduce_kernel<HD, OUT_MODE>, dim3((uint32_t)rows), dim3(HD / 2), 0, a.stream, (const float*)a.b[0].ptr,
                                            a.b[1].ptr, n_splits, 0);
     ++*a.launches;
     return check_cuda(a, e, "attn_reduce");
@@ -509,7 +467,7 @@ int launch_combine_ranks_d128(const LaunchArgs& a)
         return fail_validation(a, "attn_combine_ranks: rows must be > 0 and n_ranks in 1..1024");
     if (int r = need_bytes(a, 0, rows * n_ranks * 130 * 4, "gathered partials")) return r;
     if (int r = need_bytes(a, 1, rows * 128 * 4, "out")) return r;
-    reduce_kernel<128, 1><<<(uint32_t)rows, 128, 0, a.stream>>>((const float*)a.b[0].ptr, a.b[1].ptr, n_ranks, 1);
+    reduce_kernel<128, 1><<<(uint32_t)rows, 64, 0, a.stream>>>((const float*)a.b[0].ptr, a.b[1].ptr, n_ranks, 1);
     ++*a.launches;
     return check_cuda(a, cudaGetLastError(), "attn_combine_ranks_d128");
 }
@@ -538,7 +496,7 @@ int launch_prefill_generic(const LaunchArgs& a)
     if (int r = need_bytes(a, bi, m * n_q * HD * (OUT_F32 ? 4 : 2), "out")) return r;
     if (int r = need_bytes(a, bi + 1, 16, "step")) return r;
     prefill_generic_kernel<HD, G, FMT_F16, FMT_F16, TWO_RANGE, OUT_F32><<<dim3(n_kv, (uint32_t)m), GEN_THREADS, 0, a.stream>>>(
-        (const __half*)a.b[0].ptr, kh, vh, kc, vc, a.b[bi].ptr, (const uint32_t*)a.b[bi + 1].ptr, WINDOW, RING, scale,
+        a.b[0].ptr, nullptr, kh, vh, kc, vc, a.b[bi].ptr, (const uint32_t*)a.b[bi + 1].ptr, WINDOW, RING, scale,
         a.status);
     ++*a.launches;
     return check_cuda(a, cudaGetLastError(), "attn_prefill");
@@ -575,9 +533,74 @@ int launch_prefill_paged_q8kv_scalar_d128(const LaunchArgs& a)
     if (int r = need_bytes(a, 7, 16, "step")) return r;
     KvOperand none{};
     prefill_generic_kernel<128, 2, FMT_Q8, FMT_Q8, 0, 1><<<dim3(n_kv, (uint32_t)m), GEN_THREADS, 0, a.stream>>>(
-        (const __half*)a.b[0].ptr, kop, vop, none, none, a.b[6].ptr, (const uint32_t*)a.b[7].ptr, 0, 0, p.scale, a.status);
+        a.b[0].ptr, nullptr, kop, vop, none, none, a.b[6].ptr, (const uint32_t*)a.b[7].ptr, 0, 0, p.scale, a.status);
     ++*a.launches;
     return check_cuda(a, cudaGetLastError(), "attn_prefill_paged_q8kv_scalar_d128");
 }
+
+// The reference's tiled global-prefill names (crates/sg-gpu/build.rs:2207-2287), all hd 512 / 4 kv heads /
+// 8 query heads per kv head, out f16, push {scale}, grid [32 query heads, M / 16] (one workgroup per query
+// head and 16-row tile, attn_prefill_global_flash_sp.wgsl:68-75).  They differ in what they bind:
+//   VARIANT 0  attn_prefill_global_flash, attn_prefill_global_flash_sp: q f16, k f16, v f16, out, step
+//   VARIANT 1  attn_prefill_global_flash_sp_q8: q f16, k_quants, k_scales, v_quants, v_scales, out, step
+//   VARIANT 2  attn_prefill_global_flash_sp_iq: q_i8, q_scales, k_quants, k_scales, v f16, out, step
+// Served by the streaming kernel on the dequantised values (the reference's own test compares the int8
+// kernel with attention over the dequantised Q and K, tests/parity_attn.rs:689-768).  Rows past the last
+// visible key are never read, so K/V need not be padded to a 64-key tile as the reference's callers do.
+template <int VARIANT>
+int launch_prefill_global_flash_ref(const LaunchArgs& a)
+{
+    constexpr int HD = 512, G = 8, N_KV = 4, M_Q = 16;
+    const float scale = *(const float*)a.push;
+    if (a.groups[0] != (uint32_t)(N_KV * G) || a.groups[1] == 0)
+        return fail_validation(a, "attn_prefill_global_flash*: groups must be [32 query heads, M / 16]");
+    const size_t m = (size_t)a.groups[1] * M_Q, n_q = (size_t)N_KV * G;
+    KvOperand kop, vop, none{};
+    const __half* q_scales = nullptr;
+    int bi = 1;
+    if (VARIANT == 2) {
+        if (a.b[0].bytes < m * n_q * HD || a.b[1].bytes < m * n_q * (HD / 32) * 2)
+            return fail_validation(a, "attn_prefill_global_flash_sp_iq: q_i8 / q_scales too small for M rows");
+        q_scales = (const __half*)a.b[1].ptr;
+        bi = 2;
+    } else if (a.b[0].bytes < m * n_q * HD * 2) {
+        return fail_validation(a, "attn_prefill_global_flash*: q buffer too small");
+    }
+    if (VARIANT == 0) {
+        kop = linear_f16(a.b[bi], N_KV, HD);
+        vop = linear_f16(a.b[bi + 1], N_KV, HD);
+        bi += 2;
+    } else {
+        kop = linear_q8(a.b[bi], a.b[bi + 1], N_KV, HD);
+        if (a.b[bi + 1].bytes / 2 < kop.rows * N_KV * (HD / 32)) return fail_validation(a, "attn_prefill_global_flash*: k_scales too short");
+        bi += 2;
+        if (VARIANT == 1) {
+            vop = linear_q8(a.b[bi], a.b[bi + 1], N_KV, HD);
+            if (a.b[bi + 1].bytes / 2 < vop.rows * N_KV * (HD / 32)) return fail_validation(a, "attn_prefill_global_flash*: v_scales too short");
+            bi += 2;
+        } else {
+            vop = linear_f16(a.b[bi++], N_KV, HD);
+        }
+    }
+    if (int r = need_bytes(a, bi, m * n_q * HD * 2, "out")) return r;
+    if (int r = need_bytes(a, bi + 1, 16, "step")) return r;
+    const dim3 grid(N_KV, (uint32_t)m);
+    void* out = a.b[bi].ptr;
+    const uint32_t* step = (const uint32_t*)a.b[bi + 1].ptr;
+    if (VARIANT == 0)
+        prefill_generic_kernel<HD, G, FMT_F16, FMT_F16, 0, 0><<<grid, GEN_THREADS, 0, a.stream>>>(a.b[0].ptr, nullptr, kop, vop, none, none, out,
+                                                                                               step, 0, 0, scale, a.status);
+    else if (VARIANT == 1)
+        prefill_generic_kernel<HD, G, FMT_Q8_F16, FMT_Q8_F16, 0, 0><<<grid, GEN_THREADS, 0, a.stream>>>(a.b[0].ptr, nullptr, kop, vop, none, none,
+                                                                                                     out, step, 0, 0, scale, a.status);
+    else
+        prefill_generic_kernel<HD, G, FMT_Q8, FMT_F16, 0, 0, FMT_Q8><<<grid, GEN_THREADS, 0, a.stream>>>(a.b[0].ptr, q_scales, kop, vop, none,
+                                                                                                      none, out, step, 0, 0, scale, a.status);
+    ++*a.launches;
+    return check_cuda(a, cudaGetLastError(), "attn_prefill_global_flash*");
+}
+template int launch_prefill_global_flash_ref<0>(const LaunchArgs&);
+template int launch_prefill_global_flash_ref<1>(const LaunchArgs&);
+template int launch_prefill_global_flash_ref<2>(const LaunchArgs&);
 
 }  // namespace sgb

@@ -1,0 +1,114 @@
+// Measurement aid, not part of the attention path: how many SM cycles one tcgen05.mma of the shapes the
+// prefill kernels issue takes when nothing but its operands limits it.  Every CTA issues `n_mma`
+// instructions back to back from one thread (operands resident in shared / tensor memory, contents
+// irrelevant), commits, waits (bounded) and reports clock64() deltas.  Shapes:
+//   0  SS  M128 x N64  x K16   (Q K^T with 64-key tiles: 4 KB of A + 2 KB of B from shared memory)
+//   1  SS  M128 x N128 x K16   (Q K^T with 128-key tiles: 4 KB + 4 KB)
+//   2  TS  M128 x N128 x K16   (P V: A from tensor memory, 4 KB of B from shared memory)
+//   3  the 128-key tile's mix: 8 x shape 1, then 8 x shape 2, repeated
+// With ctas_per_sm = 2 two CTAs share an SM's tensor pipe, as in the prefill kernels.
+#include <string>
+
+#include "sgb_common.cuh"
+#include "sgb_kernels.h"
+
+namespace sgb {
+namespace {
+
+constexpr uint32_t PROBE_SMEM = 96 * 1024;
+
+__global__ void __launch_bounds__(64, 2) mma_probe_kernel(int shape, uint32_t n_mma, unsigned long long* __restrict__ cycles, uint32_t* status)
+{
+    extern __shared__ __align__(1024) uint8_t smem_raw[];
+    __shared__ uint64_t done_bar;
+    __shared__ uint32_t tmem_base;
+    const int tid = threadIdx.x, warp = tid >> 5;
+    // operands: f16 1.0 everywhere (finite, so the result stays finite whatever n_mma is not an issue: D is overwritten
+    // by the first MMA of every group of eight)
+    for (uint32_t i = tid; i < PROBE_SMEM / 4; i += blockDim.x) reinterpret_cast<uint32_t*>(smem_raw)[i] = 0x3C003C00u;
+    if (tid == 0) {
+        mbar_init(&done_bar, 1);
+        mbar_fence_init();
+    }
+    if (warp == 0) {
+        tmem_alloc(&tmem_base, 256);
+        tmem_relinquish();
+    }
+    fence_proxy_async_smem();
+    tc_fence_before_sync();
+    __syncthreads();
+    tc_fence_after_sync();
+    const uint32_t tmem = tmem_base;
+    if (warp == 0) {  // the A operand of the TS shapes: 64 columns of packed f16 ones
+        uint32_t ones[32];
+#pragma unroll
+        for (int i = 0; i < 32; i++) ones[i] = 0x3C003C00u;
+        tmem_st_32x32b_x32(tmem, ones);
+        tmem_st_32x32b_x32(tmem + 32, ones);
+        tc_wait_st();
+    }
+    tc_fence_before_sync();
+    __syncthreads();
+    tc_fence_after_sync();
+    bool failed = false;
+    if (tid == 0) {
+        const uint32_t a_base = smem_u32(smem_raw), b_base = a_base + 32768, v_base = a_base + 65536;
+        constexpr uint32_t ID_N64 = umma_idesc_f16(128, 64, 0, 0), ID_N128 = umma_idesc_f16(128, 128, 0, 0),
+                           ID_PV = umma_idesc_f16(128, 128, 0, 1);
+        const long long t0 = clock64();
+        for (uint32_t i = 0; i < n_mma; i += 8) {
+            const bool ts = shape == 2 || (shape == 3 && ((i >> 3) & 1));
+#pragma unroll
+            for (int u = 0; u < 8; u++) {
+                if (ts) {
+                    const uint64_t db = umma_desc_sw128(v_base + u * 2048, 16384, 1024);
+                    umma_f16_ts(tmem + 128, tmem + u * 8, db, ID_PV, u ? 1u : 0u);
+                } else {
+                    const int h = u >> 2, kk = u & 3;
+                    const uint64_t da = umma_desc_sw128(a_base + h * 16384 + kk * 32, 16, 1024);
+                    const uint64_t db = umma_desc_sw128(b_base + h * 16384 + kk * 32, 16, 1024);
+                    umma_f16_ss(tmem, da, db, shape == 0 ? ID_N64 : ID_N128, u ? 1u : 0u);
+                }
+            }
+        }
+        umma_commit(&done_bar);
+        const long long t_issued = clock64();
+        mbar_wait(&done_bar, 0, status, 901, failed);
+        const long long t1 = clock64();
+        cycles[2 * blockIdx.x] = (unsigned long long)(t1 - t0);
+        cycles[2 * blockIdx.x + 1] = (unsigned long long)(t_issued - t0);
+    }
+    tc_fence_before_sync();
+    __syncthreads();
+    if (warp == 0) tmem_dealloc(tmem, 256);
+}
+
+struct PushProbe {
+    uint32_t shape, n_mma;
+};
+
+}  // namespace
+
+// diag_mma_cycles: cycles u64[2 x CTAs] (per CTA: cycles until all MMAs completed, cycles until all were issued).
+// push {shape u32, n_mma u32 (multiple of 8)}.  grid [ctas_per_sm (1 or 2)]: SMs x ctas_per_sm CTAs are launched.
+int launch_diag_mma_cycles(const LaunchArgs& a)
+{
+    const PushProbe p = *(const PushProbe*)a.push;
+    const uint32_t per_sm = a.groups[0];
+    if (p.shape > 3 || p.n_mma == 0 || (p.n_mma & 7) || p.n_mma > (1u << 20) || per_sm < 1 || per_sm > 2)
+        return fail_validation(a, "diag_mma_cycles: shape 0..3, n_mma a multiple of 8 up to 2^20, groups[0] = CTAs per SM (1 or 2)");
+    const uint32_t ctas = (uint32_t)a.sm_count * per_sm;
+    if (int r = need_bytes(a, 0, (size_t)ctas * 16, "cycles")) return r;
+    static bool attr_set[64] = {};
+    if (a.device < 64 && !attr_set[a.device]) {
+        if (int r = check_cuda(a, cudaFuncSetAttribute(mma_probe_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)PROBE_SMEM),
+                               "cudaFuncSetAttribute(mma_probe)"))
+            return r;
+        attr_set[a.device] = true;
+    }
+    mma_probe_kernel<<<ctas, 64, PROBE_SMEM, a.stream>>>((int)p.shape, p.n_mma, (unsigned long long*)a.b[0].ptr, a.status);
+    ++*a.launches;
+    return check_cuda(a, cudaGetLastError(), "diag_mma_cycles");
+}
+
+}  // namespace sgb

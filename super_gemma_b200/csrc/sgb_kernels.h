@@ -94,9 +94,11 @@ template <int HD, int OUT_MODE> int launch_reduce(const LaunchArgs&);
 int launch_combine_ranks_d128(const LaunchArgs&);
 template <int HD, int G, int WINDOW, int RING, int TWO_RANGE, int OUT_F32> int launch_prefill_generic(const LaunchArgs&);
 int launch_prefill_paged_q8kv_scalar_d128(const LaunchArgs&);
+template <int VARIANT> int launch_prefill_global_flash_ref(const LaunchArgs&);
 
 // attn_exchange.cu
 int launch_reduce_exchange_d128(const LaunchArgs&);
+int launch_reduce_exchange_timed_d128(const LaunchArgs&);
 
 // attn_decode_paged.cu
 int launch_decode_paged_q8kv_d128(const LaunchArgs&);
@@ -105,5 +107,8 @@ int launch_decode_paged_q8kv_d128(const LaunchArgs&);
 int launch_prefill_flash_f16_d128(const LaunchArgs&);
 int launch_prefill_sliding_ring_flash_d128(const LaunchArgs&);
 int launch_prefill_paged_q8kv_flash_d128(const LaunchArgs&);
+
+// mma_probe.cu
+int launch_diag_mma_cycles(const LaunchArgs&);
 
 }  // namespace sgb

@@ -43,6 +43,23 @@ const KernelEntry REGISTRY[] = {
     {"attn_prefill_global", {64, 1, 1}, 5, 4,
      "q f16[M x32x512], k f16[token x4x512], v, out f16, step | push {scale} | grid [4, M]; causal [0, q0+i]",
      launch_prefill_generic<512, 8, 0, 0, 0, 0>},
+    // The tiled global-prefill variants (build.rs:2207-2287): grid [32 query heads, M / 16], K/V padded to a 64-key tile
+    // by the reference's callers (not required here).  sg-model dispatches ..._flash_sp_iq for every global prefill layer
+    // (crates/sg-model/src/graph.rs:1210-1223).
+    {"attn_prefill_global_flash", {64, 1, 1}, 5, 4,
+     "q f16[M x32x512], k f16[token x4x512], v, out f16[M x32x512], step | push {scale} | grid [32, M/16]; causal [0, q0+i]",
+     launch_prefill_global_flash_ref<0>},
+    {"attn_prefill_global_flash_sp", {64, 1, 1}, 5, 4,
+     "q f16[M x32x512], k f16[token x4x512], v, out f16[M x32x512], step | push {scale} | grid [32, M/16]; causal [0, q0+i]",
+     launch_prefill_global_flash_ref<0>},
+    {"attn_prefill_global_flash_sp_q8", {64, 1, 1}, 7, 4,
+     "q f16[M x32x512], k_quants i8[token x4x512], k_scales f16[token x4x16], v_quants, v_scales, out f16, step | push {scale} | "
+     "grid [32, M/16]; K and V enter as f16(scale*q)",
+     launch_prefill_global_flash_ref<1>},
+    {"attn_prefill_global_flash_sp_iq", {64, 1, 1}, 7, 4,
+     "q_i8 i8[M x32x512], q_scales f16[M x32x16], k_quants i8[token x4x512], k_scales f16[token x4x16], v f16[token x4x512], out f16, step | "
+     "push {scale} | grid [32, M/16]; scores from the exact products f32(scale)*f32(q) of Q and K",
+     launch_prefill_global_flash_ref<2>},
     {"kv_append_sliding", {256, 1, 1}, 3, 0, "src f16[n x4096], dst f16[1024 x4096], step | grid covers src; slot = (step[0]+token) % 1024",
      launch_kv_append<4096, 1024>},
     {"kv_append_global", {256, 1, 1}, 3, 0, "src f16[n x2048], dst f16[slots x2048], step | slot = step[0]+token",
@@ -122,11 +139,16 @@ const KernelEntry REGISTRY[] = {
     {"kv_append_paged_q8_d128", {256, 1, 1}, 5, 8,
      "src f16[n x row_len], scales f16, quants i8, page_table u32, step | push {row_len u32, page u32} | row via page table from step[0]+token",
      launch_kv_append_paged_q8_d128},
-    {"attn_reduce_exchange_d128", {128, 1, 1}, 4, 12,
+    {"attn_reduce_exchange_d128", {64, 1, 1}, 4, 16,
      "part f32[rows x n_splits x 130], xbuf (this rank's exchange buffer: f32[2][world][rows][130], u32[2][world][rows], u32[rows], zeroed once), "
-     "peers u64[world] (every rank's xbuf, rank order), out f32[rows x128] | push {n_splits u32, world u32, rank u32} | grid [rows]; "
-     "merges the local splits, stores the row into every rank's buffer over NVLink, waits (bounded) for all ranks' rows, merges in rank order",
+     "peers u64[world] (every rank's xbuf, rank order), out f32[rows x128] | push {n_splits u32, world u32, rank u32, wait_us u32 (0 = about a second)} | "
+     "grid [rows]; merges the local splits, stores the row into every rank's buffer over NVLink, waits (bounded) for all ranks' rows, merges in "
+     "rank order.  After SGB_ERR_TIMEOUT the row's epoch is not advanced: re-zero every rank's xbuf under a host barrier before reuse",
      launch_reduce_exchange_d128},
+    {"attn_reduce_exchange_timed_d128", {64, 1, 1}, 5, 16,
+     "bindings and push of attn_reduce_exchange_d128, then stamps u64[rows x 5]: GPU global timer (ns) at entry, after the local merge, after the "
+     "peer stores and flags, after the wait, at the end",
+     launch_reduce_exchange_timed_d128},
     {"attn_norm_rope_d128", {256, 1, 1}, 4, 12,
      "x f16[token x n_heads x128], w f32[128], cos_sin f32[token x rot/2 x2], y f16 | push {n_heads u32, rot_dims u32 (multiple of 16), plus_one u32} | "
      "RMS norm per head, then rotate-half RoPE of the first rot_dims/2 pairs (i, i+64); rounds to f16 after each, like the two-kernel chain",
@@ -144,6 +166,12 @@ const KernelEntry REGISTRY[] = {
     {"kv_dequant_paged_q8_d128", {256, 1, 1}, 5, 8,
      "scales f16, quants i8, page_table u32, dst f16[rows x row_len], step | push {row_len, page} | first step[2] tokens, gathered to linear f16; rows up to the next multiple of 64 zeroed",
      launch_kv_dequant_paged_q8_d128},
+    // ---- measurement aid -----------------------------------------------------------------------------------------
+    {"diag_mma_cycles", {64, 1, 1}, 1, 8,
+     "cycles u64[2 x SMs x groups[0]] (per CTA: cycles until n_mma back-to-back tcgen05.mma completed, cycles until they were issued) | "
+     "push {shape u32 (0: SS M128xN64xK16, 1: SS M128xN128xK16, 2: TS M128xN128xK16, 3: 8 of shape 1 then 8 of shape 2, repeated), "
+     "n_mma u32} | grid [CTAs per SM: 1 or 2]; not part of the attention path",
+     launch_diag_mma_cycles},
 };
 
 }  // namespace

@@ -53,7 +53,7 @@ def main():
             dist.all_gather_into_tensor(gathered, mine)
         stream.synchronize()
         ctx.dispatch_blocking(comb, B(wrap(gathered), wrap(out_nccl)), world, [rows, 1, 1])
-        ctx.dispatch_blocking(fused, B(b_part, wrap(xbuf), wrap(peers), wrap(out_fused)), (n_splits, world, rank), [rows, 1, 1])
+        ctx.dispatch_blocking(fused, B(b_part, wrap(xbuf), wrap(peers), wrap(out_fused)), (n_splits, world, rank, 0), [rows, 1, 1])
         same = torch.equal(out_nccl.view(torch.int32), out_fused.view(torch.int32))
         finite = bool(torch.isfinite(out_fused).all())
         ok = ok and same and finite

@@ -37,13 +37,16 @@ def test_library_exports_every_declared_symbol(sg):
 
 def test_registry_keeps_the_reference_contract(sg):
     """Names, binding counts and push sizes of the reference's variants
-    (crates/sg-gpu/build.rs:253-437): a caller written against sg-gpu binds them unchanged."""
+    (crates/sg-gpu/build.rs:253-437, 2207-2287): a caller written against sg-gpu binds them unchanged."""
     reg = {k.name: k for k in sg.kernels()}
     ref = {
         "attn_decode_sliding": (5, 8), "attn_decode_global": (5, 8), "attn_decode_global_q8k": (6, 8),
         "attn_reduce_d256": (2, 4), "attn_reduce_d512": (2, 4), "attn_prefill_sliding": (5, 4),
         "attn_prefill_sliding_ring": (7, 4), "attn_prefill_global": (5, 4), "kv_append_sliding": (3, 0),
         "kv_append_global": (3, 0), "kv_append_global_q8": (4, 0), "kv_quant_q8": (3, 0), "kv_dequant_q8": (3, 0),
+        # the tiled global-prefill variants (build.rs:2207-2287); sg-model dispatches ..._flash_sp_iq (graph.rs:1210-1223)
+        "attn_prefill_global_flash": (5, 4), "attn_prefill_global_flash_sp": (5, 4), "attn_prefill_global_flash_sp_q8": (7, 4),
+        "attn_prefill_global_flash_sp_iq": (7, 4),
     }
     for name, (bindings, push) in ref.items():
         assert name in reg, name

@@ -33,7 +33,7 @@ def test_single_rank_exchange_equals_plain_reduce():
         p = ctx.buffer_from_iter(part.reshape(-1))
         want, got = ctx.new_buffer(rows * D, np.float32), ctx.new_buffer(rows * D, np.float32)
         ctx.dispatch_blocking(red, bind(p, want), n_splits, [rows, 1, 1])
-        ctx.dispatch_blocking(fused, bind(p, xbuf, peers, got), (n_splits, 1, 0), [rows, 1, 1])
+        ctx.dispatch_blocking(fused, bind(p, xbuf, peers, got), (n_splits, 1, 0, 0), [rows, 1, 1])
         assert np.array_equal(got.read().view(np.uint32), want.read().view(np.uint32)), f"step {step}"
     words = xbuf.read().view(np.uint32)
     assert np.all(words[-rows:] == 5)  # the per-row epoch counts the launches
@@ -49,9 +49,9 @@ def test_rejects_bad_arguments():
     out = ctx.new_buffer(32 * D, np.float32)
     peers = ctx.new_buffer(1, np.uint64)
     with pytest.raises(sg.Validation):
-        ctx.dispatch_blocking(k, bind(part, small, peers, out), (2, 1, 0), [32, 1, 1])  # exchange buffer too small
+        ctx.dispatch_blocking(k, bind(part, small, peers, out), (2, 1, 0, 0), [32, 1, 1])  # exchange buffer too small
     with pytest.raises(sg.Validation):
-        ctx.dispatch_blocking(k, bind(part, small, peers, out), (2, 2, 2), [32, 1, 1])  # rank outside the world
+        ctx.dispatch_blocking(k, bind(part, small, peers, out), (2, 2, 2, 0), [32, 1, 1])  # rank outside the world
 
 
 def test_two_ranks_match_the_nccl_path():
@@ -66,7 +66,7 @@ def test_two_ranks_match_the_nccl_path():
 
 
 def test_absent_peer_ends_in_a_timeout_status_not_a_hang():
-    """The wait for a peer's row is bounded (about a second): with a second rank that never stores its row the kernel
+    """The wait for a peer's row is bounded (the push block's wait_us, here 50 ms; about a second by default): with a second rank that never stores its row the kernel
     gives up, reports DEV_ERR_TIMEOUT through the status word, writes NaN (never stale data), and the context stays
     usable.  The absent peer is a second local buffer that nothing writes; no GPU is faulted or hung."""
     import super_gemma_b200 as sg
@@ -82,10 +82,10 @@ def test_absent_peer_ends_in_a_timeout_status_not_a_hang():
     out = ctx.new_buffer(rows * D, np.float32)
     fused = ctx.load_kernel("attn_reduce_exchange_d128")
     with pytest.raises(sg.Timeout):
-        ctx.dispatch_blocking(fused, bind(ctx.buffer_from_iter(part.reshape(-1)), mine, peers, out), (n_splits, 2, 0), [rows, 1, 1])
+        ctx.dispatch_blocking(fused, bind(ctx.buffer_from_iter(part.reshape(-1)), mine, peers, out), (n_splits, 2, 0, 50_000), [rows, 1, 1])
     assert np.all(np.isnan(out.read()))
     # the context is still good: the single-rank form runs right after
     solo = ctx.new_buffer(sharding.exchange_words(1, rows), np.float32)
     solo_peers = ctx.buffer_from_iter(np.array([solo.device_ptr], np.uint64))
-    ctx.dispatch_blocking(fused, bind(ctx.buffer_from_iter(part.reshape(-1)), solo, solo_peers, out), (n_splits, 1, 0), [rows, 1, 1])
+    ctx.dispatch_blocking(fused, bind(ctx.buffer_from_iter(part.reshape(-1)), solo, solo_peers, out), (n_splits, 1, 0, 0), [rows, 1, 1])
     assert np.all(np.isfinite(out.read()))

@@ -100,6 +100,43 @@ def test_attn_prefill_global_matches_reference(ctx, q0):  # parity_attn.rs:435
     assert_close(got[:, heads], want, 1e-2, 1e-2, f"prefill_global q0={q0}")
 
 
+# ---- the reference's tiled global-prefill names: grid [32 query heads, M / 16], K/V padded to a 64-key tile -------------
+@pytest.mark.parametrize("name", ["attn_prefill_global_flash", "attn_prefill_global_flash_sp", "attn_prefill_global_flash_sp_q8",
+                                  "attn_prefill_global_flash_sp_iq"])
+def test_attn_prefill_global_flash_names_match_reference(ctx, name):
+    """parity_attn.rs:519 (flash), :604 (flash_sp), :689 (flash_sp_iq): seed 0xA7C, m = 64, q0 in {0, 200}, heads
+    {0, 7, 15, 31}, 1e-2 / 1e-2.  The int8 form is compared with attention over the dequantised Q and K, as the
+    reference does (:756-768); the reference holds no test for ..._flash_sp_q8, which is held here to the same bar
+    against attention over f16(scale * q) of K and V."""
+    n_kv, hd, m, M_Q, N_K = 4, 512, 64, 16, 64
+    rng = O.Rng(0xA7C)
+    b16 = lambda x: ctx.buffer_from_iter(O.f32_to_f16_bits(x))
+    for q0 in (0, 200):
+        l_pad = ((q0 + m - 1) // N_K + 1) * N_K
+        q = O.through_f16(rng.f32_vec(m * N_Q * hd))
+        k = O.through_f16(rng.f32_vec(l_pad * n_kv * hd))
+        v = O.through_f16(rng.f32_vec(l_pad * n_kv * hd))
+        q_ref, k_ref, v_ref = q, k, v
+        if name.endswith("_iq"):
+            qs, qq, q_ref = O.q8_quant_div(q)
+            ks, kq, k_ref = O.q8_quant_div(k)
+            bufs = [ctx.buffer_from_iter(qq), ctx.buffer_from_iter(qs), ctx.buffer_from_iter(kq), ctx.buffer_from_iter(ks), b16(v)]
+        elif name.endswith("_q8"):
+            ks, kq, _ = O.q8_quant_div(k)
+            vs, vq, _ = O.q8_quant_div(v)
+            k_ref, v_ref = O.f16_bits_to_f32(O.dequant_q8_0_f16(ks, kq)), O.f16_bits_to_f32(O.dequant_q8_0_f16(vs, vq))
+            bufs = [b16(q), ctx.buffer_from_iter(kq), ctx.buffer_from_iter(ks), ctx.buffer_from_iter(vq), ctx.buffer_from_iter(vs)]
+        else:
+            bufs = [b16(q), b16(k), b16(v)]
+        out = ctx.new_buffer(m * N_Q * hd, np.uint16)
+        ctx.dispatch_blocking(ctx.load_kernel(name), bind(*bufs, out, _step(ctx, q0=q0)), 0.044194174, [N_Q, m // M_Q, 1])
+        got = O.f16_bits_to_f32(out.read()).reshape(m, N_Q, hd)
+        heads = [0, 7, 15, 31]
+        want = O.attention_f64(q_ref.reshape(m, N_Q, hd), k_ref.reshape(l_pad, n_kv, hd), v_ref.reshape(l_pad, n_kv, hd), m, q0, N_Q,
+                               n_kv, hd, 0.044194174, heads=heads)
+        assert_close(got[:, heads], want, 1e-2, 1e-2, f"{name} q0={q0}")
+
+
 # ---- head_dim 128: tcgen05 flash over linear f16 K/V ---------------------------------------------------
 def _linear_case(ctx, seed, m, q0, n_kv=KV):
     L = q0 + m
