@@ -445,18 +445,43 @@ def run_decode(dev, rank, world, steps, warmup, dist, ctx_len, m_q, n_splits, se
             dist.all_gather_into_tensor(gathered, mine)
         dev.ctx.dispatch(comb, dev.bind(b_gath, b_out), world, [rows, 1, 1])
 
+    tickets = torch.zeros(KV, dtype=torch.int32, device=dev.device)
+    b_tick = W(tickets)
+    decf, decx = dev.kernel("attn_decode_paged_q8kv_fused_d128"), dev.kernel("attn_decode_paged_q8kv_xchg_d128")
+
+    def step_one_launch(timer, base):  # decode + combine (+ exchange) in ONE kernel
+        kq, ks, vq, vs, tab = b_pools[base % len(b_pools)]
+        if timer is not None:
+            timer.stamp(base)
+        if world == 1:
+            dev.ctx.dispatch(decf, dev.bind(b_q, kq, ks, vq, vs, tab, b_part, b_tick, b_out, b_step), (n_splits, SCALE, PAGE), [KV, n_splits, m_q])
+        else:
+            dev.ctx.dispatch(decx, dev.bind(b_q, kq, ks, vq, vs, tab, b_part, b_tick, b_x, b_peers, b_out, b_step),
+                             (n_splits, SCALE, PAGE, world, rank, 0), [KV, n_splits, m_q])
+
     tail0 = tail_local if world == 1 else tail_nccl
-    # the decode kernel alone (a stamp between the two kernels), then the whole step with nothing between them
-    _, deltas, _ = timed(dev, make_step(True, tail0), steps, warmup, dist, stamps_per_step=2, graph=(world == 1))
-    total_s, _, launches = timed(dev, make_step(False, tail0), steps, warmup, dist, stamps_per_step=1, graph=(world == 1))
     kv_bytes = ctx_len * KV * (D + 8) * 2  # quants + scales, K and V
     algo = kv_bytes + m_q * H * D * 2 + m_q * H * D * 4 + (ctx_len // PAGE) * 4
+    # the decode kernel alone (a stamp between the two kernels), then the whole step with nothing between them
+    _, deltas, _ = timed(dev, make_step(True, tail0), steps, warmup, dist, stamps_per_step=2, graph=(world == 1))
+    total_2, _, _ = timed(dev, make_step(False, tail0), steps, warmup, dist, stamps_per_step=1, graph=(world == 1))
     kern_us = float(np.median(deltas[:, 0])) * 1e-3
-    res = {"us_per_step": total_s / steps * 1e6, "gbs": algo * steps / total_s / 1e9, "kernel_us": kern_us,
-           "kernel_gbs": (algo / world) / kern_us / 1e3, "algorithmic_bytes": algo, "n_splits": n_splits, "launches": launches}
-    if world > 1:
-        # The same step with the combine and the exchange in ONE kernel over peer memory (attn_reduce_exchange_d128)
-        # instead of reduce + NCCL all-gather + combine; no collective call, so it replays as a CUDA graph.
+    res = {"kernel_us": kern_us, "kernel_gbs": (algo / world) / kern_us / 1e3, "algorithmic_bytes": algo, "n_splits": n_splits}
+    if world == 1:
+        total_s, _, launches = timed(dev, step_one_launch, steps, warmup, dist, stamps_per_step=1, graph=True)
+        res.update({"us_per_step": total_s / steps * 1e6, "gbs": algo * steps / total_s / 1e9, "launches": launches,
+                    "two_kernel_us_per_step": total_2 / steps * 1e6,
+                    "step": "attn_decode_paged_q8kv_fused_d128 (decode + combine in one launch); two_kernel_* = decode, then attn_reduce_f32_d128"})
+        # correctness of what was just timed: same pool through both forms, bit for bit
+        make_step(False, tail_local)(None, 0)
+        dev.ctx.sync()
+        ref = out.clone()
+        out.zero_()
+        step_one_launch(None, 0)
+        dev.ctx.sync()
+        res["fused_agrees"] = bool(torch.equal(ref.view(torch.int32), out.view(torch.int32))) and bool(torch.isfinite(out).all())
+    else:
+        res.update({"nccl_us_per_step": total_2 / steps * 1e6, "nccl_gbs": algo * steps / total_2 / 1e9})
         try:
             from super_gemma_b200 import sharding
 
@@ -467,18 +492,21 @@ def run_decode(dev, rank, world, steps, warmup, dist, ctx_len, m_q, n_splits, se
             def tail_fused():
                 dev.ctx.dispatch(fx, dev.bind(b_part, b_x, b_peers, b_out), (n_splits, world, rank, 0), [rows, 1, 1])
 
-            total_f, _, launches_f = timed(dev, make_step(False, tail_fused), steps, warmup, dist, stamps_per_step=1, graph=True)
-            res.update({"nccl_us_per_step": res["us_per_step"], "nccl_gbs": res["gbs"], "us_per_step": total_f / steps * 1e6,
-                        "gbs": algo * steps / total_f / 1e9, "launches": launches_f,
-                        "exchange": f"one kernel, peer stores over NVLink ({keep[1]}); nccl_* = reduce + all-gather + combine"})
-            # Correctness of what was just timed: the same pool through both arms, compared bit for bit on every rank.
-            make_step(False, tail_nccl)(None, 0)
-            dev.ctx.sync()
-            out_nccl = out.clone()
-            out.zero_()
-            make_step(False, tail_fused)(None, 0)
-            dev.ctx.sync()
-            same = bool(torch.equal(out_nccl.view(torch.int32), out.view(torch.int32))) and bool(torch.isfinite(out).all())
+            total_f, _, _ = timed(dev, make_step(False, tail_fused), steps, warmup, dist, stamps_per_step=1, graph=True)
+            total_s, _, launches = timed(dev, step_one_launch, steps, warmup, dist, stamps_per_step=1, graph=True)
+            res.update({"us_per_step": total_s / steps * 1e6, "gbs": algo * steps / total_s / 1e9, "launches": launches,
+                        "two_launch_us_per_step": total_f / steps * 1e6,
+                        "step": f"attn_decode_paged_q8kv_xchg_d128: decode, combine and exchange over NVLink peer stores ({keep[1]}) in one launch; "
+                                "two_launch_* = decode, then attn_reduce_exchange_d128; nccl_* = decode, reduce, all-gather, combine"})
+            # Correctness of what was just timed: the same pool through all three forms, compared bit for bit on every rank.
+            outs = []
+            for form in (make_step(False, tail_nccl), make_step(False, tail_fused), step_one_launch):
+                out.zero_()
+                form(None, 0)
+                dev.ctx.sync()
+                dist.barrier()
+                outs.append(out.clone())
+            same = all(bool(torch.equal(outs[0].view(torch.int32), o.view(torch.int32))) for o in outs[1:]) and bool(torch.isfinite(outs[2]).all())
             flag = torch.tensor([1 if same else 0], device=dev.device)
             dist.all_reduce(flag, op=dist.ReduceOp.MIN)
             res["exchange_agrees"] = bool(flag.item() == 1)
@@ -502,7 +530,7 @@ def run_decode(dev, rank, world, steps, warmup, dist, ctx_len, m_q, n_splits, se
             dist.all_reduce(wait_max, op=dist.ReduceOp.MAX)
             res["exchange_phases_us"] = {"local_merge": med[0], "peer_stores_and_flags": med[1], "wait": med[2], "rank_merge": med[3],
                                          "wait_max_over_rows_and_ranks": float(wait_max.item()),
-                                         "note": "rank 0's medians over rows and replays, last of eight graph-replayed steps"}
+                                         "note": "attn_reduce_exchange_timed_d128: rank 0's medians over rows and replays, last of eight graph-replayed steps"}
         except Exception as e:
             res["fused_exchange_error"] = repr(e)
     return res
@@ -529,12 +557,13 @@ def run_decode_block(dev, steps, warmup, ctx_len, n_splits, seed, chunk=4096):
     out = torch.zeros(H * D, dtype=torch.float32, device=dev.device)
     step_t = torch.tensor([ctx_len - 1, 0, ctx_len, 0], dtype=torch.int32, device=dev.device)  # the token lands in the last row
     k1, v1 = k_raw[:1].contiguous(), v_raw[:1].contiguous()
+    tickets = torch.zeros(KV, dtype=torch.int32, device=dev.device)
     torch.cuda.synchronize()
     W = dev.wrap
-    b = {n: W(t) for n, t in dict(q_raw=q_raw, k1=k1, v1=v1, q_w=q_w, k_w=k_w, cs=cos_sin, q=q, part=part, out=out, step=step_t, kq=kq, ks=ks,
+    b = {n: W(t) for n, t in dict(q_raw=q_raw, k1=k1, v1=v1, q_w=q_w, k_w=k_w, cs=cos_sin, q=q, part=part, out=out, step=step_t, tickets=tickets, kq=kq, ks=ks,
                                   vq=vq, vs=vs, table=table).items()}
     qkv, fused = dev.kernel("qkv_norm_rope_append_paged_q8_d128"), dev.kernel("kv_norm_rope_append_paged_q8_d128")
-    dec, red = dev.kernel("attn_decode_paged_q8kv_d128"), dev.kernel("attn_reduce_f32_d128")
+    dec = dev.kernel("attn_decode_paged_q8kv_fused_d128")
     row = KV * D
 
     def step(timer, base):
@@ -542,12 +571,11 @@ def run_decode_block(dev, steps, warmup, ctx_len, n_splits, seed, chunk=4096):
             timer.stamp(base)
         dev.ctx.dispatch(qkv, dev.bind(b["q_raw"], b["q_w"], b["q"], b["k1"], b["v1"], b["k_w"], b["cs"], b["ks"], b["kq"], b["vs"], b["vq"],
                                        b["table"], b["step"]), (H, row, PAGE, D, 0), [1, 1, 1])
-        dev.ctx.dispatch(dec, dev.bind(b["q"], b["kq"], b["ks"], b["vq"], b["vs"], b["table"], b["part"], b["step"]), (n_splits, SCALE, PAGE),
-                         [KV, n_splits, 1])
-        dev.ctx.dispatch(red, dev.bind(b["part"], b["out"]), n_splits, [H, 1, 1])
+        dev.ctx.dispatch(dec, dev.bind(b["q"], b["kq"], b["ks"], b["vq"], b["vs"], b["table"], b["part"], b["tickets"], b["out"], b["step"]),
+                         (n_splits, SCALE, PAGE), [KV, n_splits, 1])
 
     total_s, _, launches = timed(dev, step, steps, warmup, None, stamps_per_step=1, graph=True)
-    res = {"us_per_token": total_s / steps * 1e6, "launches": launches, "kernels_per_token": 3, "ctx": ctx_len, "n_splits": n_splits,
+    res = {"us_per_token": total_s / steps * 1e6, "launches": launches, "kernels_per_token": 2, "ctx": ctx_len, "n_splits": n_splits,
            "note": "one cache copy: parts of the 143 MB stream may be served from the 126 MB L2"}
     # the fused append alone, on a prefill chunk written at positions 0..chunk-1
     step0 = torch.zeros(4, dtype=torch.int32, device=dev.device)
@@ -716,19 +744,21 @@ def main():
                 hint = dev.ctx.decode_splits_hint(KV, 32768)
                 for ns in sorted({32, 64, hint}):
                     d3 = run_decode(dev, rank, world, 40, 5, dist, 32768, 1, ns, 0x5603)
-                    if best is None or d3["kernel_us"] < best["kernel_us"]:
+                    if best is None or d3["us_per_step"] < best["us_per_step"]:
                         best = d3
-                best["hbm_frac_kernel"] = best["kernel_gbs"] / pk["hbm_gbs"]
+                best["hbm_frac_kernel"], best["hbm_frac_step"] = best["kernel_gbs"] / pk["hbm_gbs"], best["gbs"] / pk["hbm_gbs"]
                 extra["config3_decode_32k"] = best
                 torch.cuda.empty_cache()
                 d4 = run_decode(dev, rank, world, 40, 5, dist, 65536, 4, dev.ctx.decode_splits_hint(KV, 65536), 0x5604, copies=2)
-                d4["hbm_frac_kernel"] = d4["kernel_gbs"] / pk["hbm_gbs"]
+                d4["hbm_frac_kernel"], d4["hbm_frac_step"] = d4["kernel_gbs"] / pk["hbm_gbs"], d4["gbs"] / pk["hbm_gbs"]
                 extra["config4_verify_64k"] = d4
                 torch.cuda.empty_cache()
                 extra["decode_block_32k"] = run_decode_block(dev, 40, 5, 32768, dev.ctx.decode_splits_hint(KV, 32768), 0x5606)
                 torch.cuda.empty_cache()
             d5 = run_decode(dev, rank, world, 40, 5, dist, 131072, 1, dev.ctx.decode_splits_hint(KV, 131072 // world), 0x5605, copies=2)
             d5["hbm_frac_kernel"] = d5["kernel_gbs"] / pk["hbm_gbs"]
+            if "gbs" in d5:
+                d5["hbm_frac_step"] = d5["gbs"] / pk["hbm_gbs"] / world
             extra["config5b_decode_128k"] = d5
         except Exception as e:  # the headline line must still be printed
             extra["error"] = repr(e)

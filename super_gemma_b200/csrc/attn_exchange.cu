@@ -14,39 +14,20 @@
 // of a per-row epoch kept in the buffer: a rank can be at most one step ahead of a peer that still reads the
 // other parity, because its next step needs that peer's row of the current one.  The buffer must be zeroed
 // once, before the first use and after all ranks have allocated it.  No multimem, no TMA: plain ld/st.
-#include "attn_merge.cuh"
-#include "sgb_common.cuh"
+#include "attn_exchange.cuh"
 #include "sgb_kernels.h"
 
 namespace sgb {
 
 namespace {
 
-constexpr int HD = 128;
-constexpr int ROWF = HD + 2;
+constexpr int HD = XCHG_HD;
+constexpr int ROWF = XCHG_ROWF;
 constexpr int XCHG_MAX_SPLITS = 1024;
 constexpr int XCHG_MAX_RANKS = 64;
 
-__device__ __forceinline__ void st_release_sys(uint32_t* p, uint32_t v)
-{
-    asm volatile("st.release.sys.global.u32 [%0], %1;" ::"l"(p), "r"(v) : "memory");
-}
-__device__ __forceinline__ uint32_t ld_acquire_sys(const uint32_t* p)
-{
-    uint32_t v;
-    asm volatile("ld.acquire.sys.global.u32 %0, [%1];" : "=r"(v) : "l"(p) : "memory");
-    return v;
-}
-
-// Exchange buffer of one rank, in 4-byte words: data f32[2][world][rows][130], flags u32[2][world][rows],
-// epoch u32[rows].
-__host__ __device__ inline size_t xchg_words(size_t world, size_t rows) { return 2 * world * rows * ROWF + 2 * world * rows + rows; }
-
-// The wait limit is a launch argument (cycles of the SM clock) so that a host whose ranks may launch far
-// apart can raise it; 0 means the library's default of about a second.  After a timeout the row is NaN and
-// the row's epoch is NOT advanced: the next launch on this buffer fails fast on the same flag instead of
-// overwriting a slot that a slow peer may still read.  The host must then re-zero every rank's exchange
-// buffer under a barrier before using it again.
+// One CTA of 64 threads per row.  The wait limit is a launch argument (cycles of the SM clock) so that a host
+// whose ranks may launch far apart can raise it; 0 means the library's default of about a second.
 __global__ void __launch_bounds__(HD / 2) reduce_exchange_kernel(const float* __restrict__ part, float* xbuf,
                                                                  const unsigned long long* __restrict__ peers, float* __restrict__ out,
                                                                  uint32_t n_splits, uint32_t world, uint32_t rank, long long wait_cycles,
@@ -54,56 +35,18 @@ __global__ void __launch_bounds__(HD / 2) reduce_exchange_kernel(const float* __
 {
     __shared__ uint32_t timed_out;
     const size_t row = blockIdx.x, rows = gridDim.x;
-    const int t = threadIdx.x, d0 = 2 * t;
+    const int t = threadIdx.x;
     if (t == 0) timed_out = 0;
     unsigned long long t_phase[5];
-    if (stamps != nullptr && t == 0) t_phase[0] = globaltimer_ns();
-
-    // ---- 1. the local splits of this row, ascending, running maximum -------------------------------------------
+    const bool stamp = stamps != nullptr && t == 0;
+    if (stamp) t_phase[0] = globaltimer_ns();
+    __syncthreads();
+    // the local splits of this row, ascending, running maximum
     float acc[2];
-    MergeState st = merge_splits_running<HD, 2>(part + row * n_splits * ROWF, ROWF, n_splits, d0, acc);
-    if (stamps != nullptr && t == 0) t_phase[1] = globaltimer_ns();
-
-    // ---- 2. hand the merged row to every rank (this one included) ---------------------------------------------
-    const size_t flags_off = 2 * (size_t)world * rows * ROWF, epoch_off = flags_off + 2 * (size_t)world * rows;
-    uint32_t* my_words = reinterpret_cast<uint32_t*>(xbuf);
-    const uint32_t epoch = my_words[epoch_off + row] + 1;  // written only by this row's CTA of the previous launch
-    const uint32_t parity = epoch & 1;
-    const size_t slot = ((size_t)parity * world + rank) * rows + row;
-    for (uint32_t p = 0; p < world; p++) {
-        float* dst = reinterpret_cast<float*>(peers[p]) + slot * ROWF;
-        *reinterpret_cast<float2*>(dst + d0) = make_float2(acc[0], acc[1]);
-        if (t == 0) *reinterpret_cast<float2*>(dst + HD) = make_float2(st.m, st.l);
-    }
-    __threadfence_system();
-    __syncthreads();
-    if ((uint32_t)t < world) st_release_sys(reinterpret_cast<uint32_t*>(peers[t]) + flags_off + slot, epoch);
-    if (stamps != nullptr && t == 0) t_phase[2] = globaltimer_ns();
-
-    // ---- 3. wait for the same row of every rank, with a limit ----------------------------------------------------
-    if ((uint32_t)t < world) {
-        const uint32_t* flag = my_words + flags_off + ((size_t)parity * world + t) * rows + row;
-        const long long limit = wait_cycles > 0 ? wait_cycles : WAIT_LIMIT_CYCLES;
-        const long long t0 = clock64();
-        while (ld_acquire_sys(flag) != epoch) {
-            if (clock64() - t0 > limit) {
-                timed_out = 1;
-                report_error(status, DEV_ERR_TIMEOUT, 601, (uint32_t)row, (uint32_t)t);
-                break;
-            }
-            __nanosleep(100);
-        }
-    }
-    __syncthreads();
-    if (stamps != nullptr && t == 0) t_phase[3] = globaltimer_ns();
-
-    // ---- 4. merge the ranks in rank order (same arithmetic as the splits; ld.cg: written by other GPUs) ---------
-    st = merge_splits_running<HD, 2>(xbuf + ((size_t)parity * world * rows + row) * ROWF, rows * ROWF, world, d0, acc);
-    const bool bad = timed_out != 0;
-    const float nan = __int_as_float(0x7fc00000);  // a row that gave up is NaN, never stale data
-    *reinterpret_cast<float2*>(out + row * HD + d0) = bad ? make_float2(nan, nan) : make_float2(acc[0] / st.l, acc[1] / st.l);
-    if (t == 0 && !bad) my_words[epoch_off + row] = epoch;
-    if (stamps != nullptr && t == 0) {
+    const MergeState st = merge_splits_running<HD, 2>(part + row * n_splits * ROWF, ROWF, n_splits, 2 * t, acc);
+    if (stamp) t_phase[1] = globaltimer_ns();
+    exchange_row(acc, st, row, rows, t, 1, &timed_out, xbuf, peers, world, rank, wait_cycles, status, out, stamp ? t_phase + 2 : nullptr);
+    if (stamp) {
         t_phase[4] = globaltimer_ns();
         for (int i = 0; i < 5; i++) stamps[row * 5 + i] = t_phase[i];
     }

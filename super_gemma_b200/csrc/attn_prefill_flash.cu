@@ -53,6 +53,21 @@ constexpr uint32_t TMEM_S = 0;     // S: two buffers of 64 f32 columns
 constexpr uint32_t TMEM_O = 128;   // O: 128 f32 columns
 constexpr float RESCALE_T = 8.0f;
 
+// Build with -DSGB_FLASH_STAMPS to make the first four CTAs of kv head 0 add up, per role, the SM cycles spent in each
+// phase of a key tile (sgb_debug_flash_stamps copies the sums out).  Off in the shipped library.
+#ifdef SGB_FLASH_STAMPS
+}  // namespace
+__device__ unsigned long long g_flash_stamps[4][16];
+namespace {
+#define STAMP_DECL long long st_t = clock64(); unsigned long long st_sum[6] = {0, 0, 0, 0, 0, 0};
+#define STAMP(k) { const long long st_n = clock64(); st_sum[k] += (unsigned long long)(st_n - st_t); st_t = st_n; }
+#define STAMP_DUMP(base, n) if (blockIdx.y == 0 && blockIdx.z == 0 && blockIdx.x < 4) { for (int st_i = 0; st_i < n; st_i++) g_flash_stamps[blockIdx.x][base + st_i] = st_sum[st_i]; }
+#else
+#define STAMP_DECL
+#define STAMP(k)
+#define STAMP_DUMP(base, n)
+#endif
+
 // 96 KB of tiles + 128 B of barriers.  Two CTAs must fit in the SM's 228 KB next to the 1 KB the
 // system reserves per CTA, so the struct is NOT padded to its 1024-byte tile alignment: the dynamic
 // shared-memory base is declared 1024-aligned instead (and checked at run time).
@@ -237,21 +252,25 @@ __global__ void __launch_bounds__(FLASH_THREADS, 2) flash_prefill_kernel(const _
         if ((tid & 31) == 0) {
             constexpr uint32_t IDESC_QK = umma_idesc_f16(BLOCK_M, BLOCK_N, 0, 0);
             constexpr uint32_t IDESC_PV = umma_idesc_f16(BLOCK_M, HD, 0, 1);
+            // Operand descriptors are built once; a step of 32 bytes along K (or of 16 keys of V) is an add to the
+            // descriptor's address field (bytes >> 4).  Building them per instruction costs the issuing thread more
+            // cycles than the tensor pipe needs for the instruction.
+            const uint64_t dq[2] = {umma_desc_sw128(smem_u32(sm.q[0]), 16, 1024), umma_desc_sw128(smem_u32(sm.q[1]), 16, 1024)};
+            const uint64_t dk[2][2] = {{umma_desc_sw128(smem_u32(sm.k[0][0]), 16, 1024), umma_desc_sw128(smem_u32(sm.k[0][1]), 16, 1024)},
+                                       {umma_desc_sw128(smem_u32(sm.k[1][0]), 16, 1024), umma_desc_sw128(smem_u32(sm.k[1][1]), 16, 1024)}};
+            const uint64_t dv[2] = {umma_desc_sw128(smem_u32(sm.v[0][0]), HALF_TILE, 1024), umma_desc_sw128(smem_u32(sm.v[1][0]), HALF_TILE, 1024)};
             // S[j % 2] = Q K(j)^T: 8 MMAs of K = 16, once K(j) has landed.
             auto issue_qk = [&](int j) {
                 const int b = j % KV_STAGES;
                 mbar_wait(&sm.full_k[b], (j / KV_STAGES) & 1, prm.status, 402, failed);
                 if (failed) return;
                 tc_fence_after_sync();
+                const uint64_t k0 = b ? dk[1][0] : dk[0][0], k1 = b ? dk[1][1] : dk[0][1];
+                const uint32_t d = tmem + TMEM_S + b * BLOCK_N;
 #pragma unroll
-                for (int h = 0; h < 2; h++) {
+                for (int kk = 0; kk < 4; kk++) umma_f16_ss(d, dq[0] + 2 * kk, k0 + 2 * kk, IDESC_QK, kk ? 1u : 0u);
 #pragma unroll
-                    for (int kk = 0; kk < 4; kk++) {
-                        const uint64_t da = umma_desc_sw128(smem_u32(sm.q[h]) + kk * 32, 16, 1024);
-                        const uint64_t db = umma_desc_sw128(smem_u32(sm.k[b][h]) + kk * 32, 16, 1024);
-                        umma_f16_ss(tmem + TMEM_S + b * BLOCK_N, da, db, IDESC_QK, (h | kk) ? 1u : 0u);
-                    }
-                }
+                for (int kk = 0; kk < 4; kk++) umma_f16_ss(d, dq[1] + 2 * kk, k1 + 2 * kk, IDESC_QK, 1u);
                 umma_commit(&sm.s_ready[b]);
             };
             mbar_wait(&sm.q_bar, 0, prm.status, 401, failed);
@@ -263,11 +282,13 @@ __global__ void __launch_bounds__(FLASH_THREADS, 2) flash_prefill_kernel(const _
                 mbar_wait(&sm.full_v[b], (j / KV_STAGES) & 1, prm.status, 405, failed);
                 if (failed) break;
                 tc_fence_after_sync();
-#pragma unroll
-                for (int kk = 0; kk < 4; kk++) {
+                {
                     // P(j) lives in the first 32 columns of S[b] (packed f16 pairs), written by the softmax warps
-                    const uint64_t db = umma_desc_sw128(smem_u32(sm.v[b][0]) + kk * 2048, HALF_TILE, 1024);
-                    umma_f16_ts(tmem + TMEM_O, tmem + TMEM_S + b * BLOCK_N + kk * 8, db, IDESC_PV, (j | kk) ? 1u : 0u);
+                    const uint64_t v0 = b ? dv[1] : dv[0];
+                    const uint32_t pa = tmem + TMEM_S + b * BLOCK_N;
+                    umma_f16_ts(tmem + TMEM_O, pa, v0, IDESC_PV, j ? 1u : 0u);
+#pragma unroll
+                    for (int kk = 1; kk < 4; kk++) umma_f16_ts(tmem + TMEM_O, pa + kk * 8, v0 + 128 * kk, IDESC_PV, 1u);
                 }
                 umma_commit(&sm.pv_done[b]);
                 if (j + 2 < n_tiles) {
@@ -593,35 +614,39 @@ __global__ void __launch_bounds__(FLASH_THREADS, 2) flash128_prefill_kernel(cons
         if ((tid & 31) == 0) {
             constexpr uint32_t IDESC_QK = umma_idesc_f16(BLOCK_M, BN2, 0, 0);
             constexpr uint32_t IDESC_PV = umma_idesc_f16(BLOCK_M, HD, 0, 1);
+            // operand descriptors built once; a K step of 32 bytes / a V step of 16 keys is an add to the address field
+            const uint64_t dq[2] = {umma_desc_sw128(smem_u32(sm.q[0]), 16, 1024), umma_desc_sw128(smem_u32(sm.q[1]), 16, 1024)};
+            const uint64_t dk[2] = {umma_desc_sw128(smem_u32(sm.k[0]), 16, 1024), umma_desc_sw128(smem_u32(sm.k[1]), 16, 1024)};
+            const uint64_t dv = umma_desc_sw128(smem_u32(sm.v[0]), KV2_HALF, 1024);
             mbar_wait(&sm.q_bar, 0, prm.status, 421, failed);
+            STAMP_DECL
             for (int j = 0; j < n_tiles; ++j) {
                 // S = Q K(j)^T.  S is free: PV(j-1), which read P out of it, was issued before and the tensor
                 // pipe runs in order.
                 mbar_wait(&sm.full_k, j & 1, prm.status, 422, failed);
                 if (failed) break;
                 tc_fence_after_sync();
+                STAMP(0)
 #pragma unroll
-                for (int h = 0; h < 2; h++) {
+                for (int kk = 0; kk < 4; kk++) umma_f16_ss(tmem + T2_S, dq[0] + 2 * kk, dk[0] + 2 * kk, IDESC_QK, kk ? 1u : 0u);
 #pragma unroll
-                    for (int kk = 0; kk < 4; kk++) {
-                        const uint64_t da = umma_desc_sw128(smem_u32(sm.q[h]) + kk * 32, 16, 1024);
-                        const uint64_t db = umma_desc_sw128(smem_u32(sm.k[h]) + kk * 32, 16, 1024);
-                        umma_f16_ss(tmem + T2_S, da, db, IDESC_QK, (h | kk) ? 1u : 0u);
-                    }
-                }
+                for (int kk = 0; kk < 4; kk++) umma_f16_ss(tmem + T2_S, dq[1] + 2 * kk, dk[1] + 2 * kk, IDESC_QK, 1u);
                 umma_commit(&sm.s_ready);
+                STAMP(1)
                 // O += P(j) V(j): P as the TMEM A operand (two keys per column), V as the MN-major B operand
                 mbar_wait(&sm.p_ready, j & 1, prm.status, 423, failed);
+                STAMP(2)
                 mbar_wait(&sm.full_v, j & 1, prm.status, 425, failed);
                 if (failed) break;
                 tc_fence_after_sync();
+                STAMP(3)
+                umma_f16_ts(tmem + T2_O, tmem + T2_S, dv, IDESC_PV, j ? 1u : 0u);
 #pragma unroll
-                for (int kk = 0; kk < 8; kk++) {
-                    const uint64_t db = umma_desc_sw128(smem_u32(sm.v[0]) + kk * 2048, KV2_HALF, 1024);
-                    umma_f16_ts(tmem + T2_O, tmem + T2_S + kk * 8, db, IDESC_PV, (j | kk) ? 1u : 0u);
-                }
+                for (int kk = 1; kk < 8; kk++) umma_f16_ts(tmem + T2_O, tmem + T2_S + kk * 8, dv + 128 * kk, IDESC_PV, 1u);
                 umma_commit(&sm.pv_done);
+                STAMP(4)
             }
+            STAMP_DUMP(0, 5)
         }
     } else {
         // ======================= softmax: row r of the tile <-> TMEM lane r <-> thread r =======================
@@ -631,6 +656,7 @@ __global__ void __launch_bounds__(FLASH_THREADS, 2) flash128_prefill_kernel(cons
         const int64_t row_lo = (prm.window != 0 && qpos + 1 > (int64_t)prm.window) ? qpos + 1 - prm.window : 0;
         const float scale2 = prm.scale * 1.4426950408889634f;  // > 0 (checked on the host)
         const uint32_t lane_addr = tmem + ((uint32_t)(warp * 32) << 16);
+        STAMP_DECL
         const uint32_t s_addr = lane_addr + T2_S, o_addr = lane_addr + T2_O;
         float m_run = NEG_SENTINEL, l_run = 0.0f;
 
@@ -651,6 +677,7 @@ __global__ void __launch_bounds__(FLASH_THREADS, 2) flash128_prefill_kernel(cons
             };
             mbar_wait(&sm.s_ready, it & 1, prm.status, 424, failed);
             tc_fence_after_sync();
+            STAMP(0)
 
             // ---- pass 1: the row maximum of the raw scores (scale2 > 0 commutes with max) ----
             float mx;
@@ -669,6 +696,7 @@ __global__ void __launch_bounds__(FLASH_THREADS, 2) flash128_prefill_kernel(cons
                 }
                 mx = fmaxf(fmaxf(mx4[0], mx4[1]), fmaxf(mx4[2], mx4[3])) * scale2;
             }
+            STAMP(1)
             const bool grow = mx > m_run + RESCALE_T;
             float corr = 1.0f;
             if (grow) {
@@ -691,6 +719,7 @@ __global__ void __launch_bounds__(FLASH_THREADS, 2) flash128_prefill_kernel(cons
                 tc_wait_st();
             }
 
+            STAMP(2)
             // ---- pass 2: p = 2^(s * scale2 - m), l += p (f32, before P is rounded to f16), P over S ----
             {
                 const float2 sc2 = make_float2(scale2, scale2), neg_m = make_float2(-m_run, -m_run);
@@ -735,9 +764,17 @@ __global__ void __launch_bounds__(FLASH_THREADS, 2) flash128_prefill_kernel(cons
                     fence_proxy_async_smem();  // generic-proxy writes, read next by the tensor pipe
                 }
             }
+            STAMP(3)
             tc_wait_st();
             tc_fence_before_sync();
             mbar_arrive(&sm.p_ready);
+            STAMP(4)
+        }
+        if (r == 0) {
+#ifdef SGB_FLASH_STAMPS
+            st_sum[5] = (unsigned long long)n_tiles;
+#endif
+            STAMP_DUMP(5, 6)
         }
         // the tensor pipe completes in order: the last P V done means all of them are
         if (n_tiles > 0) mbar_wait(&sm.pv_done, (n_tiles - 1) & 1, prm.status, 428, failed);
@@ -889,7 +926,7 @@ int run_flash(const LaunchArgs& a, const BufView& q, const BufView& k0, const Bu
     // exponential pairs per 16 that the 128-key kernel evaluates on the FMA pipe.
     static const int bn = [] {
         const char* e = getenv("SGB_FLASH_BN");
-        return e && atoi(e) == 128 ? 128 : 64;  // the 128-key kernel is opt-in until its parity run is in
+        return e && atoi(e) == 64 ? 64 : 128;
     }();
     static const int poly = [] {
         const char* e = getenv("SGB_FLASH_POLY");
@@ -1008,3 +1045,10 @@ int launch_prefill_paged_q8kv_flash_d128(const LaunchArgs& a)
 }
 
 }  // namespace sgb
+
+#ifdef SGB_FLASH_STAMPS
+extern "C" int sgb_debug_flash_stamps(unsigned long long* out)
+{
+    return (int)cudaMemcpyFromSymbol(out, sgb::g_flash_stamps, sizeof(unsigned long long) * 64);
+}
+#endif

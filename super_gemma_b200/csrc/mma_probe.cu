@@ -6,6 +6,8 @@
 //   1  SS  M128 x N128 x K16   (Q K^T with 128-key tiles: 4 KB + 4 KB)
 //   2  TS  M128 x N128 x K16   (P V: A from tensor memory, 4 KB of B from shared memory)
 //   3  the 128-key tile's mix: 8 x shape 1, then 8 x shape 2, repeated
+// Operand descriptors are built once and stepped by an add, as in the prefill kernels: the figure is the pipe's, not
+// the issuing thread's.
 // With ctas_per_sm = 2 two CTAs share an SM's tensor pipe, as in the prefill kernels.
 #include <string>
 
@@ -17,7 +19,8 @@ namespace {
 
 constexpr uint32_t PROBE_SMEM = 96 * 1024;
 
-__global__ void __launch_bounds__(64, 2) mma_probe_kernel(int shape, uint32_t n_mma, unsigned long long* __restrict__ cycles, uint32_t* status)
+template <int SHAPE>
+__global__ void __launch_bounds__(64, 2) mma_probe_kernel(uint32_t n_mma, unsigned long long* __restrict__ cycles, uint32_t* status)
 {
     extern __shared__ __align__(1024) uint8_t smem_raw[];
     __shared__ uint64_t done_bar;
@@ -55,20 +58,32 @@ __global__ void __launch_bounds__(64, 2) mma_probe_kernel(int shape, uint32_t n_
         const uint32_t a_base = smem_u32(smem_raw), b_base = a_base + 32768, v_base = a_base + 65536;
         constexpr uint32_t ID_N64 = umma_idesc_f16(128, 64, 0, 0), ID_N128 = umma_idesc_f16(128, 128, 0, 0),
                            ID_PV = umma_idesc_f16(128, 128, 0, 1);
+        constexpr uint32_t ID_SS = SHAPE == 0 ? ID_N64 : ID_N128;
+        // descriptors built once, stepped by adding to the address field (bytes >> 4), as the prefill kernels do
+        const uint64_t da[2] = {umma_desc_sw128(a_base, 16, 1024), umma_desc_sw128(a_base + 16384, 16, 1024)};
+        const uint64_t db[2] = {umma_desc_sw128(b_base, 16, 1024), umma_desc_sw128(b_base + 16384, 16, 1024)};
+        const uint64_t dv = umma_desc_sw128(v_base, 16384, 1024);
         const long long t0 = clock64();
-        for (uint32_t i = 0; i < n_mma; i += 8) {
-            const bool ts = shape == 2 || (shape == 3 && ((i >> 3) & 1));
+        for (uint32_t i = 0; i < n_mma; i += 16) {
+            if (SHAPE != 2) {
 #pragma unroll
-            for (int u = 0; u < 8; u++) {
-                if (ts) {
-                    const uint64_t db = umma_desc_sw128(v_base + u * 2048, 16384, 1024);
-                    umma_f16_ts(tmem + 128, tmem + u * 8, db, ID_PV, u ? 1u : 0u);
-                } else {
-                    const int h = u >> 2, kk = u & 3;
-                    const uint64_t da = umma_desc_sw128(a_base + h * 16384 + kk * 32, 16, 1024);
-                    const uint64_t db = umma_desc_sw128(b_base + h * 16384 + kk * 32, 16, 1024);
-                    umma_f16_ss(tmem, da, db, shape == 0 ? ID_N64 : ID_N128, u ? 1u : 0u);
-                }
+                for (int kk = 0; kk < 4; kk++) umma_f16_ss(tmem, da[0] + 2 * kk, db[0] + 2 * kk, ID_SS, kk ? 1u : 0u);
+#pragma unroll
+                for (int kk = 0; kk < 4; kk++) umma_f16_ss(tmem, da[1] + 2 * kk, db[1] + 2 * kk, ID_SS, 1u);
+            }
+            if (SHAPE >= 2) {
+#pragma unroll
+                for (int kk = 0; kk < 8; kk++) umma_f16_ts(tmem + 128, tmem + kk * 8, dv + 128 * kk, ID_PV, kk ? 1u : 0u);
+            }
+            if (SHAPE < 2) {
+#pragma unroll
+                for (int kk = 0; kk < 4; kk++) umma_f16_ss(tmem, da[0] + 2 * kk, db[0] + 2 * kk, ID_SS, kk ? 1u : 0u);
+#pragma unroll
+                for (int kk = 0; kk < 4; kk++) umma_f16_ss(tmem, da[1] + 2 * kk, db[1] + 2 * kk, ID_SS, 1u);
+            }
+            if (SHAPE == 2) {
+#pragma unroll
+                for (int kk = 0; kk < 8; kk++) umma_f16_ts(tmem + 128, tmem + kk * 8, dv + 128 * kk, ID_PV, kk ? 1u : 0u);
             }
         }
         umma_commit(&done_bar);
@@ -90,23 +105,21 @@ struct PushProbe {
 }  // namespace
 
 // diag_mma_cycles: cycles u64[2 x CTAs] (per CTA: cycles until all MMAs completed, cycles until all were issued).
-// push {shape u32, n_mma u32 (multiple of 8)}.  grid [ctas_per_sm (1 or 2)]: SMs x ctas_per_sm CTAs are launched.
+// push {shape u32, n_mma u32 (multiple of 16)}.  grid [ctas_per_sm (1 or 2)]: SMs x ctas_per_sm CTAs are launched.
 int launch_diag_mma_cycles(const LaunchArgs& a)
 {
     const PushProbe p = *(const PushProbe*)a.push;
     const uint32_t per_sm = a.groups[0];
-    if (p.shape > 3 || p.n_mma == 0 || (p.n_mma & 7) || p.n_mma > (1u << 20) || per_sm < 1 || per_sm > 2)
-        return fail_validation(a, "diag_mma_cycles: shape 0..3, n_mma a multiple of 8 up to 2^20, groups[0] = CTAs per SM (1 or 2)");
+    if (p.shape > 3 || p.n_mma == 0 || (p.n_mma & 15) || p.n_mma > (1u << 20) || per_sm < 1 || per_sm > 2)
+        return fail_validation(a, "diag_mma_cycles: shape 0..3, n_mma a multiple of 16 up to 2^20, groups[0] = CTAs per SM (1 or 2)");
     const uint32_t ctas = (uint32_t)a.sm_count * per_sm;
     if (int r = need_bytes(a, 0, (size_t)ctas * 16, "cycles")) return r;
-    static bool attr_set[64] = {};
-    if (a.device < 64 && !attr_set[a.device]) {
-        if (int r = check_cuda(a, cudaFuncSetAttribute(mma_probe_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)PROBE_SMEM),
-                               "cudaFuncSetAttribute(mma_probe)"))
-            return r;
-        attr_set[a.device] = true;
-    }
-    mma_probe_kernel<<<ctas, 64, PROBE_SMEM, a.stream>>>((int)p.shape, p.n_mma, (unsigned long long*)a.b[0].ptr, a.status);
+    typedef void (*ProbeKernel)(uint32_t, unsigned long long*, uint32_t*);
+    const ProbeKernel kern = p.shape == 0 ? mma_probe_kernel<0> : p.shape == 1 ? mma_probe_kernel<1> : p.shape == 2 ? mma_probe_kernel<2> : mma_probe_kernel<3>;
+    if (int r = check_cuda(a, cudaFuncSetAttribute((const void*)kern, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)PROBE_SMEM),
+                           "cudaFuncSetAttribute(mma_probe)"))
+        return r;
+    kern<<<ctas, 64, PROBE_SMEM, a.stream>>>(p.n_mma, (unsigned long long*)a.b[0].ptr, a.status);
     ++*a.launches;
     return check_cuda(a, cudaGetLastError(), "diag_mma_cycles");
 }

@@ -89,6 +89,16 @@ const KernelEntry REGISTRY[] = {
     {"attn_verify_paged_q8kv_d128", {160, 1, 1}, 8, 12,
      "as attn_decode_paged_q8kv_d128 with m_q = groups[2] query tokens, causal among themselves (append-then-attend)",
      launch_decode_paged_q8kv_d128},
+    {"attn_decode_paged_q8kv_fused_d128", {128, 1, 1}, 10, 12,
+     "q, k_quants, k_scales, v_quants, v_scales, page_table, part (scratch, as attn_decode_paged_q8kv_d128), tickets u32[KV] (zeroed once; "
+     "the kernel leaves it zero), out f32[m_q*H x128], step | push {n_splits, scale, page} | grid [KV, n_splits, m_q]; decode and combine in "
+     "one launch: the CTA that finishes a kv head last merges that head's splits in index order (the bits of attn_reduce_f32_d128)",
+     launch_decode_paged_q8kv_fused_d128},
+    {"attn_decode_paged_q8kv_xchg_d128", {128, 1, 1}, 12, 24,
+     "q, k_quants, k_scales, v_quants, v_scales, page_table, part, tickets u32[KV], xbuf, peers u64[world] (as attn_reduce_exchange_d128), "
+     "out f32[m_q*H x128], step | push {n_splits u32, scale f32, page u32, world u32, rank u32, wait_us u32} | grid [KV, n_splits, m_q]; "
+     "sequence-parallel decode in one launch: split-K partials, combine, exchange of the merged rows over NVLink, merge in rank order",
+     launch_decode_paged_q8kv_xchg_d128},
     {"attn_decode_paged_q8kv_scalar_d128", {128, 1, 1}, 8, 12,
      "same bindings, push and grid as attn_decode_paged_q8kv_d128; one-warp-per-key CUDA-core statement of the same math",
      launch_decode_paged_q8kv_scalar_d128},
