@@ -206,22 +206,34 @@ def check_prefill_rows(dev, out, q, kq, ks, vq, vs, table, m, q0, ctx_len, local
 
 def timed(dev, fn, steps, warmup, dist=None, stamps_per_step=1, graph=False):
     """W untimed steps, then K steps bracketed by barrier + synchronize; returns (max-over-ranks
-    seconds for the K steps, per-step stamp deltas in ns as array [K, stamps_per_step]).
+    seconds for the K steps, per-step stamp deltas in ns as array [K, stamps_per_step], launches).
     graph=True records the K steps once and replays them as one CUDA graph, the way the reference
     drives its decode step (record_graph / submit_blocking): steps of a few tens of microseconds
-    are otherwise bounded by the host's dispatch rate, not by the GPU."""
+    are otherwise bounded by the host's dispatch rate, not by the GPU.
+    stamps_per_step = 0 puts no timestamp between the steps (one before the first, one after the last; the deltas
+    are then None): an event record between two kernels of a few tens of microseconds costs microseconds of its
+    own and keeps the second kernel from being scheduled behind the first."""
     torch = dev.torch
     for _ in range(warmup):
         fn(None, 0)
     dev.ctx.sync()
-    timer = dev.ctx.new_timer(steps * stamps_per_step + 1)
-    g = None
-    if graph:
-        def record(_ctx):
+    ends_only = stamps_per_step == 0
+    timer = dev.ctx.new_timer(2 if ends_only else steps * stamps_per_step + 1)
+
+    def run_steps():
+        if ends_only:
+            timer.stamp(0)
+            for i in range(steps):
+                fn(None, i)
+            timer.stamp(1)
+        else:
             for i in range(steps):
                 fn(timer, i * stamps_per_step)
             timer.stamp(steps * stamps_per_step)
-        g = dev.ctx.record_graph(record)
+
+    g = None
+    if graph:
+        g = dev.ctx.record_graph(lambda _ctx: run_steps())
         dev.ctx.submit_blocking(g)  # one untimed replay
     if dist is not None:
         dist.barrier()
@@ -230,9 +242,7 @@ def timed(dev, fn, steps, warmup, dist=None, stamps_per_step=1, graph=False):
     if g is not None:
         dev.ctx.submit(g)
     else:
-        for i in range(steps):
-            fn(timer, i * stamps_per_step)
-        timer.stamp(steps * stamps_per_step)
+        run_steps()
     dev.ctx.sync()
     torch.cuda.synchronize()
     launches = dev.ctx.launch_count - before
@@ -242,7 +252,7 @@ def timed(dev, fn, steps, warmup, dist=None, stamps_per_step=1, graph=False):
         t = torch.tensor([total_s], dtype=torch.float64, device=dev.device)
         dist.all_reduce(t, op=dist.ReduceOp.MAX)
         total_s = float(t.item())
-    return total_s, np.diff(ns).reshape(steps, stamps_per_step), launches
+    return total_s, (None if ends_only else np.diff(ns).reshape(steps, stamps_per_step)), launches
 
 
 # --------------------------------------------------------------------------------------------------
@@ -464,11 +474,11 @@ def run_decode(dev, rank, world, steps, warmup, dist, ctx_len, m_q, n_splits, se
     algo = kv_bytes + m_q * H * D * 2 + m_q * H * D * 4 + (ctx_len // PAGE) * 4
     # the decode kernel alone (a stamp between the two kernels), then the whole step with nothing between them
     _, deltas, _ = timed(dev, make_step(True, tail0), steps, warmup, dist, stamps_per_step=2, graph=(world == 1))
-    total_2, _, _ = timed(dev, make_step(False, tail0), steps, warmup, dist, stamps_per_step=1, graph=(world == 1))
+    total_2, _, _ = timed(dev, make_step(False, tail0), steps, warmup, dist, stamps_per_step=0, graph=(world == 1))
     kern_us = float(np.median(deltas[:, 0])) * 1e-3
     res = {"kernel_us": kern_us, "kernel_gbs": (algo / world) / kern_us / 1e3, "algorithmic_bytes": algo, "n_splits": n_splits}
     if world == 1:
-        total_s, _, launches = timed(dev, step_one_launch, steps, warmup, dist, stamps_per_step=1, graph=True)
+        total_s, _, launches = timed(dev, step_one_launch, steps, warmup, dist, stamps_per_step=0, graph=True)
         res.update({"us_per_step": total_s / steps * 1e6, "gbs": algo * steps / total_s / 1e9, "launches": launches,
                     "two_kernel_us_per_step": total_2 / steps * 1e6,
                     "step": "attn_decode_paged_q8kv_fused_d128 (decode + combine in one launch); two_kernel_* = decode, then attn_reduce_f32_d128"})
@@ -492,8 +502,8 @@ def run_decode(dev, rank, world, steps, warmup, dist, ctx_len, m_q, n_splits, se
             def tail_fused():
                 dev.ctx.dispatch(fx, dev.bind(b_part, b_x, b_peers, b_out), (n_splits, world, rank, 0), [rows, 1, 1])
 
-            total_f, _, _ = timed(dev, make_step(False, tail_fused), steps, warmup, dist, stamps_per_step=1, graph=True)
-            total_s, _, launches = timed(dev, step_one_launch, steps, warmup, dist, stamps_per_step=1, graph=True)
+            total_f, _, _ = timed(dev, make_step(False, tail_fused), steps, warmup, dist, stamps_per_step=0, graph=True)
+            total_s, _, launches = timed(dev, step_one_launch, steps, warmup, dist, stamps_per_step=0, graph=True)
             res.update({"us_per_step": total_s / steps * 1e6, "gbs": algo * steps / total_s / 1e9, "launches": launches,
                         "two_launch_us_per_step": total_f / steps * 1e6,
                         "step": f"attn_decode_paged_q8kv_xchg_d128: decode, combine and exchange over NVLink peer stores ({keep[1]}) in one launch; "
@@ -574,7 +584,7 @@ def run_decode_block(dev, steps, warmup, ctx_len, n_splits, seed, chunk=4096):
         dev.ctx.dispatch(dec, dev.bind(b["q"], b["kq"], b["ks"], b["vq"], b["vs"], b["table"], b["part"], b["tickets"], b["out"], b["step"]),
                          (n_splits, SCALE, PAGE), [KV, n_splits, 1])
 
-    total_s, _, launches = timed(dev, step, steps, warmup, None, stamps_per_step=1, graph=True)
+    total_s, _, launches = timed(dev, step, steps, warmup, None, stamps_per_step=0, graph=True)
     res = {"us_per_token": total_s / steps * 1e6, "launches": launches, "kernels_per_token": 2, "ctx": ctx_len, "n_splits": n_splits,
            "note": "one cache copy: parts of the 143 MB stream may be served from the 126 MB L2"}
     # the fused append alone, on a prefill chunk written at positions 0..chunk-1
@@ -588,7 +598,7 @@ def run_decode_block(dev, steps, warmup, ctx_len, n_splits, seed, chunk=4096):
         dev.ctx.dispatch(fused, dev.bind(b_k, b_v, b["k_w"], b["cs"], b["ks"], b["kq"], b["vs"], b["vq"], b["table"], b_s0), (row, PAGE, D, 0),
                          [1, 1, 1])
 
-    total_s, _, _ = timed(dev, step_app, steps, warmup, None, stamps_per_step=1, graph=True)
+    total_s, _, _ = timed(dev, step_app, steps, warmup, None, stamps_per_step=0, graph=True)
     algo = chunk * KV * (2 * D * 2 + 2 * (D + 8))
     res["fused_append_chunk"] = {"tokens": chunk, "us": total_s / steps * 1e6, "algorithmic_bytes": algo,
                                  "gbs": algo * steps / total_s / 1e9, "note": "50 MB working set: L2-resident, not an HBM figure"}
@@ -670,6 +680,26 @@ def reference_arm(args):
     print(json.dumps(line), flush=True)
 
 
+def probe_mma(n_mma=4096):
+    """diag_mma_cycles: every CTA issues n_mma back-to-back tcgen05.mma of one shape from one thread and reports the SM
+    cycles until they have completed; one or two CTAs per SM.  One JSON line per (shape, CTAs per SM)."""
+    import super_gemma_b200 as sg
+
+    ctx = sg.GpuContext(0)
+    k = ctx.load_kernel("diag_mma_cycles")
+    sms = sg.lib().sgb_ctx_sm_count(ctx._h)
+    names = ["SS M128xN64xK16", "SS M128xN128xK16", "TS M128xN128xK16", "8 x SS M128xN128xK16 then 8 x TS M128xN128xK16"]
+    for per_sm in (1, 2):
+        for shape, name in enumerate(names):
+            buf = ctx.new_buffer(2 * sms * per_sm, np.uint64)
+            for _ in range(3):
+                ctx.dispatch_blocking(k, [sg.BufferBinding.buffer(0, buf)], (shape, n_mma), [per_sm, 1, 1])
+            c = buf.read().reshape(-1, 2).astype(np.float64) / n_mma
+            print(json.dumps({"shape": name, "ctas_per_sm": per_sm, "n_mma": n_mma, "cycles_per_mma_per_cta": float(np.median(c[:, 0])),
+                              "cycles_per_mma_per_sm": float(np.median(c[:, 0])) / per_sm, "min": float(c[:, 0].min()), "max": float(c[:, 0].max()),
+                              "issue_cycles_per_mma": float(np.median(c[:, 1]))}), flush=True)
+
+
 def workload_config(args, world):
     return {"workload": f"BASELINE config 5a: chunked prefill, {args.m} queries at q0={args.ctx - args.m} over {args.ctx} cached "
                         f"Q8_0 tokens (256-token pages, seeded random page table), 32 q / 16 kv heads, head_dim 128, causal",
@@ -688,11 +718,15 @@ def main():
     ap.add_argument("--no-extra", action="store_true", help="headline workload only")
     ap.add_argument("--no-cpu", action="store_true", help="skip the CPU baseline leg")
     ap.add_argument("--no-e2e", action="store_true", help="skip the end-to-end (host buffers) leg")
+    ap.add_argument("--probe-mma", action="store_true", help="print SM cycles per tcgen05.mma for the shapes the prefill kernels issue, and exit")
     args = ap.parse_args()
     args.warmup = max(args.warmup, 3) if args.impl == "b200" else args.warmup
 
     if args.impl == "reference":
         reference_arm(args)
+        return
+    if args.probe_mma:
+        probe_mma()
         return
 
     import torch

@@ -33,11 +33,6 @@ __device__ __forceinline__ uint32_t ld_acquire_sys(const uint32_t* p)
     asm volatile("ld.acquire.sys.global.u32 %0, [%1];" : "=r"(v) : "l"(p) : "memory");
     return v;
 }
-// Barrier `id` (1..15; 0 is __syncthreads) over `threads` threads of the CTA, a multiple of 32.
-__device__ __forceinline__ void named_barrier_sync(uint32_t id, uint32_t threads)
-{
-    asm volatile("bar.sync %0, %1;" ::"r"(id), "r"(threads) : "memory");
-}
 
 __host__ __device__ inline size_t xchg_words(size_t world, size_t rows) { return 2 * world * rows * XCHG_ROWF + 2 * world * rows + rows; }
 

@@ -4,8 +4,11 @@
 //     m_new = max(m, m_s);  ca = exp(m - m_new);  cb = exp(m_s - m_new)
 //     acc = acc * ca + acc_s * cb;  l = l * ca + l_s * cb;  m = m_new
 // so all of them produce the same bits from the same partials, and reruns are bit-identical.
-// The loads of 32 splits are issued before the dependent arithmetic on them, so the chain costs one
-// memory latency per 32 splits, not one per split.
+// The loads of 32 splits are issued together, and the part of the recurrence that is the same for every dim of a
+// row -- the running maximum and the two factors ca, cb of each split -- is taken out of the per-dim chain: lane u
+// owns split s0 + u, the running maximum is a prefix maximum over the lanes (five shuffles), every lane computes its
+// split's ca and cb at once, and what remains serial is one fused multiply-add per split and dim.  The values of m, ca,
+// cb and the order of the multiply-adds are exactly those of the sequential statement, so the bits are too.
 #pragma once
 
 #include "sgb_common.cuh"
@@ -32,33 +35,45 @@ __device__ __forceinline__ MergeState merge_splits_running(const float* row_base
 #pragma unroll
     for (int d = 0; d < N; d++) acc[d] = 0.0f;
     for (uint32_t s0 = 0; s0 < n_splits; s0 += BATCH) {
+        // Straight-line loads: indices past the end are clamped to the last split (a valid address) and their values
+        // ignored below, so that nothing stands between one load and the next and all of them are in flight together.
         float v[BATCH][N];
-        float2 ml = make_float2(NEG_SENTINEL, 0.0f);
-        if (s0 + lane < n_splits) ml = __ldcg(reinterpret_cast<const float2*>(row_base + (size_t)(s0 + lane) * s_stride + HD));
+        const uint32_t s_mine = min(s0 + lane, n_splits - 1);
+        const float2 ml = __ldcg(reinterpret_cast<const float2*>(row_base + (size_t)s_mine * s_stride + HD));
 #pragma unroll
         for (int u = 0; u < BATCH; u++) {
-            if (s0 + u < n_splits) {
-                const float* p = row_base + (size_t)(s0 + u) * s_stride + d0;
-                if constexpr (N == 2) {
-                    const float2 x = __ldcg(reinterpret_cast<const float2*>(p));
-                    v[u][0] = x.x, v[u][1] = x.y;
-                } else {
-                    v[u][0] = __ldcg(p);
-                }
+            const float* p = row_base + (size_t)min(s0 + (uint32_t)u, n_splits - 1) * s_stride + d0;
+            if constexpr (N == 2) {
+                const float2 x = __ldcg(reinterpret_cast<const float2*>(p));
+                v[u][0] = x.x, v[u][1] = x.y;
+            } else {
+                v[u][0] = __ldcg(p);
             }
         }
+        // lane u: (m, l) of split s0 + u; lanes past the end hold an empty split and are skipped below
+        const bool mine = s0 + lane < n_splits;
+        const float ms = mine ? ml.x : NEG_SENTINEL, ls = mine ? ml.y : 0.0f;
+        float pm = ms;  // inclusive prefix maximum over the lanes, then joined with the maximum carried in
+#pragma unroll
+        for (int off = 1; off < 32; off <<= 1) {
+            const float t = __shfl_up_sync(0xffffffffu, pm, off);
+            if (lane >= (uint32_t)off) pm = fmaxf(pm, t);
+        }
+        pm = fmaxf(pm, m);                                  // running maximum after this lane's split
+        float prev = __shfl_up_sync(0xffffffffu, pm, 1);    // ... and before it
+        if (lane == 0) prev = m;
+        const float ca = __expf(prev - pm), cb = __expf(ms - pm);  // empty split: exp(-3e38 - m) = 0
+        const float lcb = __fmul_rn(ls, cb);
 #pragma unroll
         for (int u = 0; u < BATCH; u++) {
-            const float ms = __shfl_sync(0xffffffffu, ml.x, u), ls = __shfl_sync(0xffffffffu, ml.y, u);
+            const float a = __shfl_sync(0xffffffffu, ca, u), b = __shfl_sync(0xffffffffu, cb, u), lb = __shfl_sync(0xffffffffu, lcb, u);
             if (s0 + u < n_splits) {
-                const float m_new = fmaxf(m, ms);
-                const float ca = __expf(m - m_new), cb = __expf(ms - m_new);  // empty split: exp(-3e38 - m) = 0
 #pragma unroll
-                for (int d = 0; d < N; d++) acc[d] = fmaf(acc[d], ca, __fmul_rn(v[u][d], cb));  // one spelling, one rounding order
-                l = fmaf(l, ca, __fmul_rn(ls, cb));
-                m = m_new;
+                for (int d = 0; d < N; d++) acc[d] = fmaf(acc[d], a, __fmul_rn(v[u][d], b));  // one spelling, one rounding order
+                l = fmaf(l, a, lb);
             }
         }
+        m = __shfl_sync(0xffffffffu, pm, 31);  // lanes past the end carry the last real maximum along
     }
     return MergeState{m, l};
 }

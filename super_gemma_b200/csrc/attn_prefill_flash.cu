@@ -53,21 +53,6 @@ constexpr uint32_t TMEM_S = 0;     // S: two buffers of 64 f32 columns
 constexpr uint32_t TMEM_O = 128;   // O: 128 f32 columns
 constexpr float RESCALE_T = 8.0f;
 
-// Build with -DSGB_FLASH_STAMPS to make the first four CTAs of kv head 0 add up, per role, the SM cycles spent in each
-// phase of a key tile (sgb_debug_flash_stamps copies the sums out).  Off in the shipped library.
-#ifdef SGB_FLASH_STAMPS
-}  // namespace
-__device__ unsigned long long g_flash_stamps[4][16];
-namespace {
-#define STAMP_DECL long long st_t = clock64(); unsigned long long st_sum[6] = {0, 0, 0, 0, 0, 0};
-#define STAMP(k) { const long long st_n = clock64(); st_sum[k] += (unsigned long long)(st_n - st_t); st_t = st_n; }
-#define STAMP_DUMP(base, n) if (blockIdx.y == 0 && blockIdx.z == 0 && blockIdx.x < 4) { for (int st_i = 0; st_i < n; st_i++) g_flash_stamps[blockIdx.x][base + st_i] = st_sum[st_i]; }
-#else
-#define STAMP_DECL
-#define STAMP(k)
-#define STAMP_DUMP(base, n)
-#endif
-
 // 96 KB of tiles + 128 B of barriers.  Two CTAs must fit in the SM's 228 KB next to the 1 KB the
 // system reserves per CTA, so the struct is NOT padded to its 1024-byte tile alignment: the dynamic
 // shared-memory base is declared 1024-aligned instead (and checked at run time).
@@ -452,711 +437,6 @@ __global__ void __launch_bounds__(FLASH_THREADS, 2) flash_prefill_kernel(const _
     if (warp == 0) tmem_dealloc(tmem, TMEM_COLS);
 }
 
-// ====================================================================================================
-// 128-key tiles.  Same roles and semantics as flash_prefill_kernel; what changes is the tile and the schedule:
-//   * S[128 x 128] = Q K^T is 8 MMAs of M128 x N128 x K16.  An SS MMA reads its A and B operands from shared
-//     memory every time: with N = 64 that is 6 KB per 32 tensor-pipe cycles, more than shared memory delivers,
-//     with N = 128 it is 8 KB per 64 cycles, which it does.
-//   * one S buffer (128 TMEM columns) + O (128 columns) per CTA, two CTAs per SM: each CTA runs the chain
-//     QK(j) -> softmax(j) -> PV(j) -> QK(j+1) serially and the two CTAs of an SM fill each other's gaps on the
-//     tensor pipe and on the special-function unit.  Every hand-off between roles is now paid once per 128 keys.
-//   * one K and one V slot of 32 KB: K(j+1) is fetched as soon as QK(j) has completed and lands while
-//     softmax(j) and PV(j) run; V(j+1) is fetched when PV(j) has completed and lands during QK(j+1), softmax(j+1).
-//   * the softmax reads its row twice from tensor memory (row max, then the exponentials 32 columns at a time)
-//     instead of holding 128 scores in registers; P overwrites the columns of S already consumed.
-//   * POLY of every 16 pairs of exponentials are evaluated on the FMA pipe (ex2_poly2) to relieve the
-//     special-function unit, which needs as many cycles per tile as the tensor pipe does.
-// ====================================================================================================
-constexpr int BN2 = 128;
-constexpr uint32_t KV2_HALF = BN2 * 128;            // one [128 keys][128 B] box
-constexpr uint32_t KV2_TILE_BYTES = 2 * KV2_HALF;
-constexpr uint32_t T2_S = 0, T2_O = 128;
-
-struct Flash128Smem {
-    uint8_t q[2][2 * HALF_TILE];   // [dim half][128 rows x 128 B]
-    uint8_t k[2][KV2_HALF];        // [dim half][128 keys x 128 B]
-    uint8_t v[2][KV2_HALF];
-    uint64_t full_k, full_v;       // TMA -> MMA warp
-    uint64_t s_ready;              // MMA commit: S holds Q K^T of a tile (and the K slot is free)
-    uint64_t p_ready;              // 128 softmax threads: P is in tensor memory
-    uint64_t pv_done;              // MMA commit: O += P V has completed (the V slot and S are free)
-    uint64_t q_bar;
-    uint32_t tmem_base;
-    uint32_t abort;
-    uint32_t pad[18];
-};
-static_assert(sizeof(Flash128Smem) == 3 * 32768 + 128, "tiles + barriers, no padding");
-static_assert(2 * (sizeof(Flash128Smem) + 1024) <= 228 * 1024, "two CTAs per SM");
-
-template <bool TWO_SRC, int POLY>
-__global__ void __launch_bounds__(FLASH_THREADS, 2) flash128_prefill_kernel(const __grid_constant__ CUtensorMap tm_q,
-                                                                            const __grid_constant__ CUtensorMap tm_k0,
-                                                                            const __grid_constant__ CUtensorMap tm_v0,
-                                                                            const __grid_constant__ CUtensorMap tm_k1,
-                                                                            const __grid_constant__ CUtensorMap tm_v1,
-                                                                            const FlashParams prm)
-{
-    extern __shared__ __align__(1024) uint8_t smem_raw[];
-    Flash128Smem& sm = *reinterpret_cast<Flash128Smem*>(smem_raw);
-    if ((smem_u32(smem_raw) & 1023u) != 0u) {
-        if (threadIdx.x == 0) report_error(prm.status, DEV_ERR_BOUNDS, 420, smem_u32(smem_raw), 0);
-        return;
-    }
-    const int tid = threadIdx.x, warp = tid >> 5;
-    const int qt = (int)gridDim.x - 1 - (int)blockIdx.x;  // longest (latest) tiles first
-    const int kvh = blockIdx.y;
-    const uint32_t m0 = (uint32_t)qt * BLOCK_TOK;
-    const int64_t q0 = prm.step[STEP_Q0];
-    const uint32_t tok_in_tile = min((uint32_t)BLOCK_TOK, prm.m_tokens - m0);
-
-    // ---- which key tiles this CTA visits (as in flash_prefill_kernel, 128 keys per tile) ------------------
-    const int64_t first_qpos = q0 + m0, last_qpos = q0 + m0 + tok_in_tile - 1;
-    const int64_t band_lo = (prm.window != 0 && first_qpos + 1 > (int64_t)prm.window) ? first_qpos + 1 - prm.window : 0;
-    const int64_t last_lo = (prm.window != 0 && last_qpos + 1 > (int64_t)prm.window) ? last_qpos + 1 - prm.window : 0;
-    const int64_t kv_last = q0 + (int64_t)prm.m_tokens - 1;  // last position that exists at all
-    int n_hist, n_tiles;
-    int64_t hist_pos0 = 0, chunk_c0 = 0;
-    if (TWO_SRC) {
-        const int64_t h_lo = band_lo, h_hi = q0;  // half-open
-        hist_pos0 = (h_lo / BN2) * BN2;
-        n_hist = h_hi > h_lo ? (int)((h_hi - 1) / BN2 - h_lo / BN2 + 1) : 0;
-        const int64_t c_lo = (band_lo > q0 ? band_lo - q0 : 0), c_hi = last_qpos - q0;  // inclusive chunk rows
-        chunk_c0 = (c_lo / BN2) * BN2;
-        n_tiles = n_hist + (int)(c_hi / BN2 - c_lo / BN2 + 1);
-    } else {
-        hist_pos0 = (band_lo / BN2) * BN2;
-        n_hist = (int)(last_qpos / BN2 - band_lo / BN2 + 1);
-        n_tiles = n_hist;
-    }
-    const int per_piece = (n_tiles + (int)gridDim.z - 1) / (int)gridDim.z;
-    const int t_begin = min(n_tiles, (int)blockIdx.z * per_piece);
-    n_tiles = min(n_tiles, t_begin + per_piece) - t_begin;
-    auto tile_at = [&](int it) {
-        Tile t;
-        it += t_begin;
-        if (it < n_hist) {
-            t.src = 0;
-            t.pos0 = hist_pos0 + (int64_t)it * BN2;
-            t.row0 = (int)(TWO_SRC ? t.pos0 % prm.ring : t.pos0);
-            t.lo = 0;
-            t.hi = TWO_SRC ? q0 - 1 : INT64_MAX;
-        } else {
-            t.src = 1;
-            const int64_t c = chunk_c0 + (int64_t)(it - n_hist) * BN2;
-            t.pos0 = q0 + c;
-            t.row0 = (int)c;
-            t.lo = q0;
-            t.hi = INT64_MAX;
-        }
-        return t;
-    };
-
-    // ---- set-up -----------------------------------------------------------------------------------------
-    if (tid == 0) {
-        mbar_init(&sm.full_k, 1);
-        mbar_init(&sm.full_v, 1);
-        mbar_init(&sm.s_ready, 1);
-        mbar_init(&sm.p_ready, SOFTMAX_THREADS);
-        mbar_init(&sm.pv_done, 1);
-        mbar_init(&sm.q_bar, 1);
-        sm.abort = 0;
-        mbar_fence_init();
-    }
-    if (warp == 0) {
-        tmem_alloc(&sm.tmem_base, TMEM_COLS);
-        tmem_relinquish();
-    }
-    tc_fence_before_sync();
-    __syncthreads();
-    tc_fence_after_sync();
-    const uint32_t tmem = sm.tmem_base;
-    bool failed = false;
-
-    if (warp == LOAD_WARP) {
-        // ======================= TMA loads =======================
-        if ((tid & 31) == 0) {
-            tma_prefetch_desc(&tm_q);
-            tma_prefetch_desc(&tm_k0);
-            tma_prefetch_desc(&tm_v0);
-            auto load_k = [&](int it) {
-                const Tile t = tile_at(it);
-                const CUtensorMap* mk = (TWO_SRC && t.src) ? &tm_k1 : &tm_k0;
-                mbar_arrive_expect_tx(&sm.full_k, KV2_TILE_BYTES);
-                tma_load_3d(sm.k[0], mk, &sm.full_k, 0, kvh, t.row0);
-                tma_load_3d(sm.k[1], mk, &sm.full_k, 64, kvh, t.row0);
-            };
-            auto load_v = [&](int it) {
-                const Tile t = tile_at(it);
-                const CUtensorMap* mv = (TWO_SRC && t.src) ? &tm_v1 : &tm_v0;
-                mbar_arrive_expect_tx(&sm.full_v, KV2_TILE_BYTES);
-                tma_load_3d(sm.v[0], mv, &sm.full_v, 0, kvh, t.row0);
-                tma_load_3d(sm.v[1], mv, &sm.full_v, 64, kvh, t.row0);
-            };
-            mbar_arrive_expect_tx(&sm.q_bar, Q_BYTES);
-            tma_load_3d(sm.q[0], &tm_q, &sm.q_bar, 0, kvh * G, (int)m0);
-            tma_load_3d(sm.q[1], &tm_q, &sm.q_bar, 64, kvh * G, (int)m0);
-            if (n_tiles > 0) {
-                load_k(0);
-                load_v(0);
-            }
-            for (int j = 0; j + 1 < n_tiles; ++j) {
-                // the K slot is free once QK(j) has completed, the V slot once PV(j) has
-                mbar_wait(&sm.s_ready, j & 1, prm.status, 431, failed, 64);
-                if (failed) break;  // never write into a slot that may still be read
-                load_k(j + 1);
-                mbar_wait(&sm.pv_done, j & 1, prm.status, 432, failed, 64);
-                if (failed) break;
-                load_v(j + 1);
-            }
-        }
-    } else if (warp == MMA_WARP) {
-        // ======================= MMA issue =======================
-        if ((tid & 31) == 0) {
-            constexpr uint32_t IDESC_QK = umma_idesc_f16(BLOCK_M, BN2, 0, 0);
-            constexpr uint32_t IDESC_PV = umma_idesc_f16(BLOCK_M, HD, 0, 1);
-            // operand descriptors built once; a K step of 32 bytes / a V step of 16 keys is an add to the address field
-            const uint64_t dq[2] = {umma_desc_sw128(smem_u32(sm.q[0]), 16, 1024), umma_desc_sw128(smem_u32(sm.q[1]), 16, 1024)};
-            const uint64_t dk[2] = {umma_desc_sw128(smem_u32(sm.k[0]), 16, 1024), umma_desc_sw128(smem_u32(sm.k[1]), 16, 1024)};
-            const uint64_t dv = umma_desc_sw128(smem_u32(sm.v[0]), KV2_HALF, 1024);
-            mbar_wait(&sm.q_bar, 0, prm.status, 421, failed);
-            STAMP_DECL
-            for (int j = 0; j < n_tiles; ++j) {
-                // S = Q K(j)^T.  S is free: PV(j-1), which read P out of it, was issued before and the tensor
-                // pipe runs in order.
-                mbar_wait(&sm.full_k, j & 1, prm.status, 422, failed);
-                if (failed) break;
-                tc_fence_after_sync();
-                STAMP(0)
-#pragma unroll
-                for (int kk = 0; kk < 4; kk++) umma_f16_ss(tmem + T2_S, dq[0] + 2 * kk, dk[0] + 2 * kk, IDESC_QK, kk ? 1u : 0u);
-#pragma unroll
-                for (int kk = 0; kk < 4; kk++) umma_f16_ss(tmem + T2_S, dq[1] + 2 * kk, dk[1] + 2 * kk, IDESC_QK, 1u);
-                umma_commit(&sm.s_ready);
-                STAMP(1)
-                // O += P(j) V(j): P as the TMEM A operand (two keys per column), V as the MN-major B operand
-                mbar_wait(&sm.p_ready, j & 1, prm.status, 423, failed);
-                STAMP(2)
-                mbar_wait(&sm.full_v, j & 1, prm.status, 425, failed);
-                if (failed) break;
-                tc_fence_after_sync();
-                STAMP(3)
-                umma_f16_ts(tmem + T2_O, tmem + T2_S, dv, IDESC_PV, j ? 1u : 0u);
-#pragma unroll
-                for (int kk = 1; kk < 8; kk++) umma_f16_ts(tmem + T2_O, tmem + T2_S + kk * 8, dv + 128 * kk, IDESC_PV, 1u);
-                umma_commit(&sm.pv_done);
-                STAMP(4)
-            }
-            STAMP_DUMP(0, 5)
-        }
-    } else {
-        // ======================= softmax: row r of the tile <-> TMEM lane r <-> thread r =======================
-        const int r = tid;
-        const uint32_t tok = m0 + (uint32_t)(r >> 1);
-        const int64_t qpos = q0 + tok;
-        const int64_t row_lo = (prm.window != 0 && qpos + 1 > (int64_t)prm.window) ? qpos + 1 - prm.window : 0;
-        const float scale2 = prm.scale * 1.4426950408889634f;  // > 0 (checked on the host)
-        const uint32_t lane_addr = tmem + ((uint32_t)(warp * 32) << 16);
-        STAMP_DECL
-        const uint32_t s_addr = lane_addr + T2_S, o_addr = lane_addr + T2_O;
-        float m_run = NEG_SENTINEL, l_run = 0.0f;
-
-        for (int it = 0; it < n_tiles; ++it) {
-            const Tile t = tile_at(it);
-            const bool tile_masked = t.pos0 + BN2 - 1 > first_qpos || t.pos0 < last_lo || t.pos0 < t.lo || t.pos0 + BN2 - 1 > t.hi;
-            const int64_t hi = min(qpos, t.hi), lo = max(row_lo, t.lo);
-            // columns [c0, c0 + 32) of this row, masked where the band or the source says so
-            auto load_chunk = [&](uint32_t (&a)[32], int c0) { tmem_ld_32x32b_x32(s_addr + c0, a); };
-            auto mask_chunk = [&](uint32_t (&a)[32], int c0) {
-                if (tile_masked) {
-#pragma unroll
-                    for (int j = 0; j < 32; j++) {
-                        const int64_t pos = t.pos0 + c0 + j;
-                        if (pos < lo || pos > hi) a[j] = 0xff800000u;  // -inf
-                    }
-                }
-            };
-            mbar_wait(&sm.s_ready, it & 1, prm.status, 424, failed);
-            tc_fence_after_sync();
-            STAMP(0)
-
-            // ---- pass 1: the row maximum of the raw scores (scale2 > 0 commutes with max) ----
-            float mx;
-            {
-                float mx4[4] = {-INFINITY, -INFINITY, -INFINITY, -INFINITY};
-                uint32_t a[2][32];
-                load_chunk(a[0], 0);
-#pragma unroll
-                for (int c = 0; c < 4; c++) {
-                    tc_wait_ld();
-                    if (c + 1 < 4) load_chunk(a[(c + 1) & 1], 32 * (c + 1));
-                    mask_chunk(a[c & 1], 32 * c);
-#pragma unroll
-                    for (int j = 0; j < 32; j += 2)
-                        mx4[(j >> 1) & 3] = max3(mx4[(j >> 1) & 3], __uint_as_float(a[c & 1][j]), __uint_as_float(a[c & 1][j + 1]));
-                }
-                mx = fmaxf(fmaxf(mx4[0], mx4[1]), fmaxf(mx4[2], mx4[3])) * scale2;
-            }
-            STAMP(1)
-            const bool grow = mx > m_run + RESCALE_T;
-            float corr = 1.0f;
-            if (grow) {
-                corr = ex2(m_run - mx);
-                m_run = mx;
-                l_run *= corr;
-            }
-            // O is rescaled where a row's maximum moved (rare after the first tiles).  O is quiescent here:
-            // S(it) is ready, so QK(it) has completed, and PV(it - 1) was issued before it.
-            if (it > 0 && __any_sync(0xffffffffu, grow)) {
-#pragma unroll
-                for (int c = 0; c < 4; c++) {
-                    uint32_t o[32];
-                    tmem_ld_32x32b_x32(o_addr + 32 * c, o);
-                    tc_wait_ld();
-#pragma unroll
-                    for (int j = 0; j < 32; j++) o[j] = __float_as_uint(__uint_as_float(o[j]) * corr);
-                    tmem_st_32x32b_x32(o_addr + 32 * c, o);
-                }
-                tc_wait_st();
-            }
-
-            STAMP(2)
-            // ---- pass 2: p = 2^(s * scale2 - m), l += p (f32, before P is rounded to f16), P over S ----
-            {
-                const float2 sc2 = make_float2(scale2, scale2), neg_m = make_float2(-m_run, -m_run);
-                float2 ls4[4] = {make_float2(0.0f, 0.0f), make_float2(0.0f, 0.0f), make_float2(0.0f, 0.0f), make_float2(0.0f, 0.0f)};
-                uint32_t a[2][32];
-                load_chunk(a[0], 0);
-#pragma unroll
-                for (int c = 0; c < 4; c++) {
-                    tc_wait_ld();
-                    if (c + 1 < 4) load_chunk(a[(c + 1) & 1], 32 * (c + 1));
-                    mask_chunk(a[c & 1], 32 * c);
-                    uint32_t pk[16];
-#pragma unroll
-                    for (int j = 0; j < 16; j++) {
-                        const float2 x = __ffma2_rn(make_float2(__uint_as_float(a[c & 1][2 * j]), __uint_as_float(a[c & 1][2 * j + 1])), sc2, neg_m);
-                        // pairs j = 16 - POLY .. 15 of every chunk go to the FMA pipe
-                        const float2 pp = (j >= 16 - POLY) ? ex2_poly2(x) : make_float2(ex2(x.x), ex2(x.y));
-                        ls4[j & 3] = __fadd2_rn(ls4[j & 3], pp);
-                        pk[j] = pack_half2(pp.x, pp.y);
-                    }
-                    // P columns [16c, 16c + 16) lie over S columns this thread has already read
-                    tmem_st_32x32b_x16(s_addr + 16 * c, pk);
-                }
-                l_run += ((ls4[0].x + ls4[0].y) + (ls4[1].x + ls4[1].y)) + ((ls4[2].x + ls4[2].y) + (ls4[3].x + ls4[3].y));
-            }
-
-            // Rows of the V tile that hold no key of this problem (past the last query's position, or past the end
-            // of the history source) are zeroed before P V reads them: their P is 0, but 0 times a stale Inf or NaN
-            // in a caller's over-allocated buffer would not be.  Only the last tile of a source can have such rows.
-            {
-                const int64_t hi_valid = min(t.hi, kv_last);
-                if (t.pos0 + BN2 - 1 > hi_valid) {  // uniform over the CTA
-                    mbar_wait(&sm.full_v, it & 1, prm.status, 429, failed);
-                    if (t.pos0 + r > hi_valid) {
-#pragma unroll
-                        for (int h = 0; h < 2; h++) {
-                            uint4* row = reinterpret_cast<uint4*>(sm.v[h] + r * 128);
-#pragma unroll
-                            for (int i = 0; i < 8; i++) row[i] = make_uint4(0u, 0u, 0u, 0u);
-                        }
-                    }
-                    fence_proxy_async_smem();  // generic-proxy writes, read next by the tensor pipe
-                }
-            }
-            STAMP(3)
-            tc_wait_st();
-            tc_fence_before_sync();
-            mbar_arrive(&sm.p_ready);
-            STAMP(4)
-        }
-        if (r == 0) {
-#ifdef SGB_FLASH_STAMPS
-            st_sum[5] = (unsigned long long)n_tiles;
-#endif
-            STAMP_DUMP(5, 6)
-        }
-        // the tensor pipe completes in order: the last P V done means all of them are
-        if (n_tiles > 0) mbar_wait(&sm.pv_done, (n_tiles - 1) & 1, prm.status, 428, failed);
-        tc_fence_after_sync();
-
-        // ---- epilogue: out = O / l, or this piece's partial (as flash_prefill_kernel) ----
-        const bool live = (uint32_t)(r >> 1) < tok_in_tile;
-        const size_t row = (size_t)(live ? tok : m0) * (prm.n_kv * G) + kvh * G + (r & 1);
-        const bool whole = gridDim.z == 1;
-        const float mul = whole ? 1.0f / l_run : 1.0f;
-        float* orow = whole ? prm.out + row * HD : prm.part_acc + (row * gridDim.z + blockIdx.z) * HD;
-        if (!whole && live) *reinterpret_cast<float2*>(prm.part_ml + (row * gridDim.z + blockIdx.z) * 2) = make_float2(m_run, l_run);
-#pragma unroll
-        for (int c = 0; c < 4; c++) {
-            uint32_t o[32];
-            if (n_tiles > 0) {  // uniform over the CTA
-                tmem_ld_32x32b_x32(o_addr + 32 * c, o);
-                tc_wait_ld();
-            } else {
-#pragma unroll
-                for (int j = 0; j < 32; j++) o[j] = 0u;  // an empty piece: m = sentinel, l = 0, O = 0
-            }
-            if (live) {
-#pragma unroll
-                for (int j = 0; j < 8; j++)
-                    *reinterpret_cast<float4*>(orow + 32 * c + 4 * j) =
-                        make_float4(__uint_as_float(o[4 * j]) * mul, __uint_as_float(o[4 * j + 1]) * mul,
-                                    __uint_as_float(o[4 * j + 2]) * mul, __uint_as_float(o[4 * j + 3]) * mul);
-            }
-        }
-    }
-    if (failed) sm.abort = 1;
-    tc_fence_before_sync();
-    __syncthreads();
-    if (*(volatile uint32_t*)&sm.abort != 0u) {
-        for (int i = 0; i < 50; i++) __nanosleep(1000);
-        __syncthreads();
-    }
-    if (warp == 0) tmem_dealloc(tmem, TMEM_COLS);
-}
-
-// ====================================================================================================
-// Two query tiles per CTA in anti-phase ("ping-pong"), 128-key tiles, one CTA per SM.
-//
-// The two single-buffered kernels above leave the tensor pipe and the special-function unit each about half
-// idle: a CTA runs QK -> softmax -> PV as a chain, and two independent CTAs on an SM fall into lockstep (both
-// in the softmax, then both queueing MMAs), so the phases add up instead of overlapping.  Here ONE CTA owns
-// two query tiles (2 x 64 tokens x the 2 heads of a kv head = 2 x 128 rows) that share every K/V tile, and the
-// MMA warp issues
-//     ... QK0(j)  PV1(j-1)  QK1(j)  PV0(j)  QK0(j+1)  PV1(j)  QK1(j+1)  PV0(j+1) ...
-// so softmax 0 of key tile j (warps 0-3) runs while the tensor pipe executes PV1(j-1) and QK1(j), and softmax 1
-// (warps 4-7) while it executes PV0(j) and QK0(j+1): the order is enforced by the data dependences themselves
-// (S_t aliases P_t, the pipe runs in order).  Tensor memory holds S0, S1, O0, O1 (4 x 128 columns).  K and V
-// tiles travel through one ring of five 32 KB slots (K0 V0 K1 V1 ...), freed by tcgen05.commit of their last
-// reader, so the TMA latency is covered by more than a key tile of work.  A softmax thread owns one row and
-// holds all 128 scores in registers (one pass: max, exponentials, row sum, P back into tensor memory).
-// Both tiles walk the union of their key ranges; the few tiles one of them does not need are masked out.
-// ====================================================================================================
-constexpr int PP_STAGES = 5;
-constexpr int PP_THREADS = 384;         // 2 x 4 softmax warps, then a warpgroup of MMA warp, load warp and two idle warps
-constexpr int PP_MMA_WARP = 8, PP_LOAD_WARP = 9;
-constexpr int PP_TOK = 2 * BLOCK_TOK;   // query tokens per CTA
-
-struct FlashPPSmem {
-    uint8_t q[2][2][2 * HALF_TILE];      // [query tile][dim half][128 rows x 128 B]
-    uint8_t kv[PP_STAGES][2][KV2_HALF];  // [slot][dim half][128 keys x 128 B]
-    uint64_t full[PP_STAGES];            // TMA -> MMA warp
-    uint64_t empty[PP_STAGES];           // MMA commit: the slot's last reader has completed
-    uint64_t s_ready[2];                 // MMA commit: S_t holds Q_t K^T of a tile
-    uint64_t p_ready[2];                 // 128 softmax threads: P_t is in tensor memory
-    uint64_t o_done[2];                  // MMA commit: the last P V of tile t has completed
-    uint64_t q_bar;
-    uint32_t tmem_base;
-    uint32_t abort;
-    uint32_t pad[28];
-};
-static_assert(sizeof(FlashPPSmem) == 2 * 32768 + PP_STAGES * 32768 + 256, "tiles + barriers");
-static_assert(sizeof(FlashPPSmem) <= 227 * 1024, "one CTA per SM");
-
-template <int POLY>
-__global__ void __launch_bounds__(PP_THREADS, 1) flash_pp_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant__ CUtensorMap tm_k,
-                                                                 const __grid_constant__ CUtensorMap tm_v, const FlashParams prm)
-{
-    extern __shared__ __align__(1024) uint8_t smem_raw[];
-    FlashPPSmem& sm = *reinterpret_cast<FlashPPSmem*>(smem_raw);
-    if ((smem_u32(smem_raw) & 1023u) != 0u) {
-        if (threadIdx.x == 0) report_error(prm.status, DEV_ERR_BOUNDS, 440, smem_u32(smem_raw), 0);
-        return;
-    }
-    const int tid = threadIdx.x, warp = tid >> 5;
-    const int qt = (int)gridDim.x - 1 - (int)blockIdx.x;  // longest (latest) tiles first
-    const int kvh = blockIdx.y;
-    const uint32_t m0 = (uint32_t)qt * PP_TOK;
-    const int64_t q0 = prm.step[STEP_Q0];
-    const uint32_t tok_in_cta = min((uint32_t)PP_TOK, prm.m_tokens - m0);
-
-    // ---- the key tiles of the CTA: the union of what its rows see ------------------------------------------
-    const int64_t first_qpos = q0 + m0, last_qpos = q0 + m0 + tok_in_cta - 1;
-    const int64_t band_lo = (prm.window != 0 && first_qpos + 1 > (int64_t)prm.window) ? first_qpos + 1 - prm.window : 0;
-    const int64_t kv_last = q0 + (int64_t)prm.m_tokens - 1;  // last position that exists at all
-    const int64_t pos_first = (band_lo / BN2) * BN2;
-    int n_tiles = (int)(last_qpos / BN2 - band_lo / BN2 + 1);
-    const int per_piece = (n_tiles + (int)gridDim.z - 1) / (int)gridDim.z;
-    const int t_begin = min(n_tiles, (int)blockIdx.z * per_piece);
-    n_tiles = min(n_tiles, t_begin + per_piece) - t_begin;
-    const int64_t pos_begin = pos_first + (int64_t)t_begin * BN2;  // position of key 0 of this CTA's tile 0
-
-    // ---- set-up -----------------------------------------------------------------------------------------
-    if (tid == 0) {
-        for (int i = 0; i < PP_STAGES; i++) {
-            mbar_init(&sm.full[i], 1);
-            mbar_init(&sm.empty[i], 1);
-        }
-        for (int i = 0; i < 2; i++) {
-            mbar_init(&sm.s_ready[i], 1);
-            mbar_init(&sm.p_ready[i], SOFTMAX_THREADS);
-            mbar_init(&sm.o_done[i], 1);
-        }
-        mbar_init(&sm.q_bar, 1);
-        sm.abort = 0;
-        mbar_fence_init();
-    }
-    if (warp == 0) {
-        tmem_alloc(&sm.tmem_base, 512);
-        tmem_relinquish();
-    }
-    tc_fence_before_sync();
-    __syncthreads();
-    tc_fence_after_sync();
-    const uint32_t tmem = sm.tmem_base;
-    bool failed = false;
-
-    // The register file is re-divided between the roles: the launch gives every thread 168 registers (65536 / 384);
-    // the warpgroup of the MMA / load warps hands most of its share to the softmax warps, which hold a whole row of
-    // 128 scores each.  8 x 32 x 200 + 4 x 32 x 96 = 63488, within the 64512 the launch already holds, so the increase can never wait for registers that do not exist.
-    // All four warps of a warpgroup must reach the SAME setmaxnreg instruction, so the branch is on the warpgroup
-    // and the roles are told apart inside it (warps 10 and 11 exist only to make the last warpgroup whole).
-    if (warp >= PP_MMA_WARP) {
-      asm volatile("setmaxnreg.dec.sync.aligned.u32 96;");
-      if (warp == PP_LOAD_WARP) {
-        // ======================= TMA loads: Q0, Q1, then K(0) V(0) K(1) V(1) ... through the ring =======================
-        if ((tid & 31) == 0) {
-            tma_prefetch_desc(&tm_q);
-            tma_prefetch_desc(&tm_k);
-            tma_prefetch_desc(&tm_v);
-            mbar_arrive_expect_tx(&sm.q_bar, 2 * Q_BYTES);
-#pragma unroll
-            for (int t = 0; t < 2; t++) {
-                tma_load_3d(sm.q[t][0], &tm_q, &sm.q_bar, 0, kvh * G, (int)m0 + t * BLOCK_TOK);
-                tma_load_3d(sm.q[t][1], &tm_q, &sm.q_bar, 64, kvh * G, (int)m0 + t * BLOCK_TOK);
-            }
-            for (int i = 0; i < 2 * n_tiles; ++i) {
-                const int slot = i % PP_STAGES;
-                if (i >= PP_STAGES) {
-                    mbar_wait(&sm.empty[slot], (i / PP_STAGES - 1) & 1, prm.status, 441, failed, 32);
-                    if (failed) break;  // never write into a slot that may still be read
-                }
-                const CUtensorMap* map = (i & 1) ? &tm_v : &tm_k;
-                const int row0 = (int)(pos_begin + (int64_t)(i >> 1) * BN2);
-                mbar_arrive_expect_tx(&sm.full[slot], KV2_TILE_BYTES);
-                tma_load_3d(sm.kv[slot][0], map, &sm.full[slot], 0, kvh, row0);
-                tma_load_3d(sm.kv[slot][1], map, &sm.full[slot], 64, kvh, row0);
-            }
-        }
-      } else if (warp == PP_MMA_WARP) {
-        // ======================= MMA issue =======================
-        if ((tid & 31) == 0) {
-            constexpr uint32_t IDESC_QK = umma_idesc_f16(BLOCK_M, BN2, 0, 0);
-            constexpr uint32_t IDESC_PV = umma_idesc_f16(BLOCK_M, HD, 0, 1);
-            // operand descriptors built once; a K step of 32 bytes / a V step of 16 keys is an add to the address field
-            const uint64_t dq[2][2] = {{umma_desc_sw128(smem_u32(sm.q[0][0]), 16, 1024), umma_desc_sw128(smem_u32(sm.q[0][1]), 16, 1024)},
-                                       {umma_desc_sw128(smem_u32(sm.q[1][0]), 16, 1024), umma_desc_sw128(smem_u32(sm.q[1][1]), 16, 1024)}};
-            const uint64_t dk_slot0 = umma_desc_sw128(smem_u32(sm.kv[0][0]), 16, 1024);       // K-major view of slot 0, dim half 0
-            const uint64_t dv_slot0 = umma_desc_sw128(smem_u32(sm.kv[0][0]), KV2_HALF, 1024);  // MN-major view of slot 0
-            constexpr uint64_t SLOT_STEP = (2 * KV2_HALF) >> 4, HALF_STEP = KV2_HALF >> 4;
-            auto issue_qk = [&](int t, int slot) {  // S_t = Q_t K^T
-                const uint64_t k0 = dk_slot0 + SLOT_STEP * slot, k1 = k0 + HALF_STEP;
-                const uint32_t d = tmem + 128 * t;
-#pragma unroll
-                for (int kk = 0; kk < 4; kk++) umma_f16_ss(d, dq[t][0] + 2 * kk, k0 + 2 * kk, IDESC_QK, kk ? 1u : 0u);
-#pragma unroll
-                for (int kk = 0; kk < 4; kk++) umma_f16_ss(d, dq[t][1] + 2 * kk, k1 + 2 * kk, IDESC_QK, 1u);
-            };
-            auto issue_pv = [&](int t, int slot, bool first) {  // O_t += P_t V
-                const uint64_t v0 = dv_slot0 + SLOT_STEP * slot;
-                const uint32_t d = tmem + 256 + 128 * t, pa = tmem + 128 * t;
-                umma_f16_ts(d, pa, v0, IDESC_PV, first ? 0u : 1u);
-#pragma unroll
-                for (int kk = 1; kk < 8; kk++) umma_f16_ts(d, pa + kk * 8, v0 + 128 * kk, IDESC_PV, 1u);
-            };
-            mbar_wait(&sm.q_bar, 0, prm.status, 442, failed);
-            STAMP_DECL
-            for (int j = 0; j < n_tiles && !failed; ++j) {
-                const int slot_k = (2 * j) % PP_STAGES, slot_v = (2 * j + 1) % PP_STAGES;
-                mbar_wait(&sm.full[slot_k], ((2 * j) / PP_STAGES) & 1, prm.status, 443, failed);
-                if (failed) break;
-                tc_fence_after_sync();
-                STAMP(0)
-                issue_qk(0, slot_k);
-                umma_commit(&sm.s_ready[0]);
-                STAMP(1)
-                if (j > 0) {
-                    // P1(j - 1) over V(j - 1), whose slot was waited for before PV0(j - 1)
-                    mbar_wait(&sm.p_ready[1], (j - 1) & 1, prm.status, 444, failed);
-                    if (failed) break;
-                    tc_fence_after_sync();
-                    STAMP(2)
-                    const int slot_pv = (2 * j - 1) % PP_STAGES;
-                    issue_pv(1, slot_pv, j == 1);
-                    umma_commit(&sm.empty[slot_pv]);
-                }
-                issue_qk(1, slot_k);
-                umma_commit(&sm.s_ready[1]);
-                umma_commit(&sm.empty[slot_k]);
-                STAMP(3)
-                mbar_wait(&sm.p_ready[0], j & 1, prm.status, 445, failed);
-                mbar_wait(&sm.full[slot_v], ((2 * j + 1) / PP_STAGES) & 1, prm.status, 446, failed);
-                if (failed) break;
-                tc_fence_after_sync();
-                STAMP(4)
-                issue_pv(0, slot_v, j == 0);
-                STAMP(5)
-            }
-            if (n_tiles > 0 && !failed) {
-                umma_commit(&sm.o_done[0]);
-                mbar_wait(&sm.p_ready[1], (n_tiles - 1) & 1, prm.status, 447, failed);
-                if (!failed) {
-                    tc_fence_after_sync();
-                    issue_pv(1, (2 * n_tiles - 1) % PP_STAGES, n_tiles == 1);
-                    umma_commit(&sm.o_done[1]);
-                }
-            }
-            STAMP_DUMP(0, 6)
-        }
-      }
-    } else {
-        // ======================= softmax: warps 0-3 own query tile 0, warps 4-7 tile 1; thread <-> row =======================
-        asm volatile("setmaxnreg.inc.sync.aligned.u32 200;");
-        const int t = warp >> 2, r = tid & 127;
-        const uint32_t tok = m0 + (uint32_t)(t * BLOCK_TOK) + (uint32_t)(r >> 1);
-        const int64_t qpos = q0 + tok;
-        const int64_t row_lo = (prm.window != 0 && qpos + 1 > (int64_t)prm.window) ? qpos + 1 - prm.window : 0;
-        // the tile-level tests use the extreme rows of THIS query tile
-        const int64_t tile_first_qpos = q0 + m0 + t * BLOCK_TOK;
-        const int64_t tile_last_qpos = tile_first_qpos + BLOCK_TOK - 1;
-        const int64_t tile_last_lo = (prm.window != 0 && tile_last_qpos + 1 > (int64_t)prm.window) ? tile_last_qpos + 1 - prm.window : 0;
-        const float scale2 = prm.scale * 1.4426950408889634f;  // > 0 (checked on the host)
-        const uint32_t lane_addr = tmem + ((uint32_t)((warp & 3) * 32) << 16);
-        const uint32_t s_addr = lane_addr + 128 * t, o_addr = lane_addr + 256 + 128 * t;
-        float m_run = NEG_SENTINEL, l_run = 0.0f;
-        STAMP_DECL
-
-        for (int it = 0; it < n_tiles; ++it) {
-            const int64_t pos0 = pos_begin + (int64_t)it * BN2;
-            const bool tile_masked = pos0 + BN2 - 1 > tile_first_qpos || pos0 < tile_last_lo;
-            mbar_wait(&sm.s_ready[t], it & 1, prm.status, 448, failed);
-            tc_fence_after_sync();
-            STAMP(0)
-            uint32_t v[128];
-#pragma unroll
-            for (int c = 0; c < 4; c++) tmem_ld_32x32b_x32(s_addr + 32 * c, *reinterpret_cast<uint32_t(*)[32]>(&v[32 * c]));
-            tc_wait_ld();
-            if (tile_masked) {
-#pragma unroll
-                for (int j = 0; j < 128; j++) {
-                    const int64_t pos = pos0 + j;
-                    if (pos < row_lo || pos > qpos) v[j] = 0xff800000u;  // -inf
-                }
-            }
-            // row max of the raw scores on four independent chains of three-input max; scale2 > 0 commutes with max
-            float mx4[4] = {__uint_as_float(v[0]), __uint_as_float(v[1]), __uint_as_float(v[2]), __uint_as_float(v[3])};
-#pragma unroll
-            for (int j = 4; j < 128; j += 2) mx4[(j >> 1) & 3] = max3(mx4[(j >> 1) & 3], __uint_as_float(v[j]), __uint_as_float(v[j + 1]));
-            const float mx = fmaxf(fmaxf(mx4[0], mx4[1]), fmaxf(mx4[2], mx4[3])) * scale2;
-            STAMP(1)
-            const bool grow = mx > m_run + RESCALE_T;
-            float corr = 1.0f;
-            if (grow) {
-                corr = ex2(m_run - mx);
-                m_run = mx;
-                l_run *= corr;
-            }
-            // O_t is rescaled where a row's maximum moved (rare after the first tiles).  O_t is quiescent here: S_t(it)
-            // is ready, so QK_t(it) has completed, and PV_t(it - 1) was issued before it.
-            if (it > 0 && __any_sync(0xffffffffu, grow)) {
-#pragma unroll
-                for (int c = 0; c < 4; c++) {
-                    uint32_t o[32];
-                    tmem_ld_32x32b_x32(o_addr + 32 * c, o);
-                    tc_wait_ld();
-#pragma unroll
-                    for (int j = 0; j < 32; j++) o[j] = __float_as_uint(__uint_as_float(o[j]) * corr);
-                    tmem_st_32x32b_x32(o_addr + 32 * c, o);
-                }
-                tc_wait_st();
-            }
-            STAMP(2)
-            // p = 2^(s * scale2 - m), l += p in f32 before P is rounded to f16 (attn_prefill_global_flash_sp.wgsl:147-156)
-            {
-                const float2 sc2 = make_float2(scale2, scale2), neg_m = make_float2(-m_run, -m_run);
-                float2 ls4[4] = {make_float2(0.0f, 0.0f), make_float2(0.0f, 0.0f), make_float2(0.0f, 0.0f), make_float2(0.0f, 0.0f)};
-#pragma unroll
-                for (int c = 0; c < 4; c++) {
-                    uint32_t pk[16];
-#pragma unroll
-                    for (int j = 0; j < 16; j++) {
-                        const float2 x = __ffma2_rn(make_float2(__uint_as_float(v[32 * c + 2 * j]), __uint_as_float(v[32 * c + 2 * j + 1])), sc2, neg_m);
-                        // pairs j = 16 - POLY .. 15 of every 16 go to the FMA pipe
-                        const float2 pp = (j >= 16 - POLY) ? ex2_poly2(x) : make_float2(ex2(x.x), ex2(x.y));
-                        ls4[j & 3] = __fadd2_rn(ls4[j & 3], pp);
-                        pk[j] = pack_half2(pp.x, pp.y);
-                    }
-                    tmem_st_32x32b_x16(s_addr + 16 * c, pk);  // P over S: every score of the row is in registers already
-                }
-                l_run += ((ls4[0].x + ls4[0].y) + (ls4[1].x + ls4[1].y)) + ((ls4[2].x + ls4[2].y) + (ls4[3].x + ls4[3].y));
-            }
-            STAMP(3)
-            // Rows of the V tile that hold no key of this problem are zeroed before P V reads them (see above); tile 0's
-            // warps do it, because PV0 is the first reader of a V tile.  Only the CTA's last tiles can have such rows.
-            if (t == 0 && pos0 + BN2 - 1 > kv_last) {  // uniform over the warps of tile 0
-                const int slot_v = (2 * it + 1) % PP_STAGES;
-                mbar_wait(&sm.full[slot_v], ((2 * it + 1) / PP_STAGES) & 1, prm.status, 449, failed);
-                if (pos0 + r > kv_last) {
-#pragma unroll
-                    for (int h = 0; h < 2; h++) {
-                        uint4* row = reinterpret_cast<uint4*>(sm.kv[slot_v][h] + r * 128);
-#pragma unroll
-                        for (int i = 0; i < 8; i++) row[i] = make_uint4(0u, 0u, 0u, 0u);
-                    }
-                }
-                fence_proxy_async_smem();  // generic-proxy writes, read next by the tensor pipe
-            }
-            tc_wait_st();
-            tc_fence_before_sync();
-            mbar_arrive(&sm.p_ready[t]);
-            STAMP(4)
-        }
-        if (r == 0 && t == 0) {
-#ifdef SGB_FLASH_STAMPS
-            st_sum[5] = (unsigned long long)n_tiles;
-#endif
-            STAMP_DUMP(6, 6)
-        }
-        if (n_tiles > 0) mbar_wait(&sm.o_done[t], 0, prm.status, 450, failed);
-        tc_fence_after_sync();
-
-        // ---- epilogue: out = O / l, or this piece's partial ----
-        const bool live = tok < prm.m_tokens;
-        const size_t row = (size_t)(live ? tok : m0) * (prm.n_kv * G) + kvh * G + (r & 1);
-        const bool whole = gridDim.z == 1;
-        const float mul = whole ? 1.0f / l_run : 1.0f;
-        float* orow = whole ? prm.out + row * HD : prm.part_acc + (row * gridDim.z + blockIdx.z) * HD;
-        if (!whole && live) *reinterpret_cast<float2*>(prm.part_ml + (row * gridDim.z + blockIdx.z) * 2) = make_float2(m_run, l_run);
-#pragma unroll
-        for (int c = 0; c < 4; c++) {
-            uint32_t o[32];
-            if (n_tiles > 0) {  // uniform over the CTA
-                tmem_ld_32x32b_x32(o_addr + 32 * c, o);
-                tc_wait_ld();
-            } else {
-#pragma unroll
-                for (int j = 0; j < 32; j++) o[j] = 0u;  // an empty piece: m = sentinel, l = 0, O = 0
-            }
-            if (live) {
-#pragma unroll
-                for (int j = 0; j < 8; j++)
-                    *reinterpret_cast<float4*>(orow + 32 * c + 4 * j) =
-                        make_float4(__uint_as_float(o[4 * j]) * mul, __uint_as_float(o[4 * j + 1]) * mul,
-                                    __uint_as_float(o[4 * j + 2]) * mul, __uint_as_float(o[4 * j + 3]) * mul);
-            }
-        }
-    }
-    if (failed) sm.abort = 1;
-    tc_fence_before_sync();
-    __syncthreads();
-    if (*(volatile uint32_t*)&sm.abort != 0u) {
-        for (int i = 0; i < 50; i++) __nanosleep(1000);
-        __syncthreads();
-    }
-    if (warp == 0) tmem_dealloc(tmem, 512);
-}
-
 // Merge the pieces of every row: out = sum_p 2^(m_p - M) O_p / sum_p 2^(m_p - M) l_p, pieces in index
 // order (fixed order => bit-identical reruns).  One warp per row, lane = 4 dims.
 constexpr int MAX_PIECES = 16;
@@ -1209,13 +489,12 @@ std::map<std::pair<int, cudaStream_t>, PieceScratch> g_piece_scratch;
 // step buffer), so the choice rests on the grid alone: with `units` equal CTAs on `slots` resident
 // places the last wave is ceil(w) - w empty; more pieces make the waves finer.  The K buffer's row
 // count bounds kv_len from above and keeps tiny problems whole.
-int choose_pieces(size_t units, int slots, size_t kv_rows_bound, int block_n)
+int choose_pieces(size_t units, int slots, size_t kv_rows_bound)
 {
     if (const char* e = getenv("SGB_FLASH_PIECES")) {
         const int v = atoi(e);
         if (v >= 1 && v <= MAX_PIECES) return v;
     }
-    (void)block_n;
     const size_t max_by_len = kv_rows_bound / 2048;  // at least 2048 keys per piece
     int best = 1;
     double best_eff = 0.0;
@@ -1263,62 +542,37 @@ int run_flash(const LaunchArgs& a, const BufView& q, const BufView& k0, const Bu
     if (out.bytes < (size_t)m_tokens * n_q * HD * 4) return fail_validation(a, "flash prefill: out buffer too small");
     if (step.bytes < 16) return fail_validation(a, "flash prefill: the step buffer holds 4 x u32");
     if (reinterpret_cast<uintptr_t>(out.ptr) & 15) return fail_validation(a, "flash prefill: out must be 16-byte aligned");
-    // Which kernel: two query tiles in anti-phase (the default for linear K/V and chunks of more than 64 tokens), or
-    // one query tile per CTA with 64- or 128-key tiles.  Tuning aids: SGB_FLASH_KERNEL = pp | 64 | 128,
-    // SGB_FLASH_POLY = 0 | 4 | 8 (exponential pairs per 16 evaluated on the FMA pipe by the 128-key kernels).
-    static const int forced_kernel = [] {
-        const char* e = getenv("SGB_FLASH_KERNEL");
-        return !e ? 0 : e[0] == 'p' ? 2 : atoi(e) == 128 ? 128 : atoi(e) == 64 ? 64 : 0;
-    }();
-    const bool pp = !TWO_SRC && (forced_kernel == 2 || (forced_kernel == 0 && m_tokens > (uint32_t)BLOCK_TOK));
-    const int bn = pp || forced_kernel == 128 ? 128 : 64;
-    static const int poly = [] {
-        const char* e = getenv("SGB_FLASH_POLY");
-        const int v = e ? atoi(e) : 4;
-        return v == 0 || v == 8 ? v : 4;
-    }();
     CUtensorMap tq, tk0, tv0, tk1, tv1;
     if (int r = encode_qkv_map(a, &tq, BufView{q.ptr, (size_t)m_tokens * n_q * HD * 2}, n_q, G, BLOCK_TOK, "q")) return r;
-    if (int r = encode_qkv_map(a, &tk0, k0, n_kv, 1, bn, "k")) return r;
-    if (int r = encode_qkv_map(a, &tv0, v0, n_kv, 1, bn, "v")) return r;
+    if (int r = encode_qkv_map(a, &tk0, k0, n_kv, 1, BLOCK_N, "k")) return r;
+    if (int r = encode_qkv_map(a, &tv0, v0, n_kv, 1, BLOCK_N, "v")) return r;
     if (TWO_SRC) {
         if (k0.bytes < (size_t)ring * n_kv * HD * 2 || v0.bytes < (size_t)ring * n_kv * HD * 2)
             return fail_validation(a, "flash prefill: ring buffers smaller than the ring");
         if (k1->bytes < (size_t)m_tokens * n_kv * HD * 2 || v1->bytes < (size_t)m_tokens * n_kv * HD * 2)
             return fail_validation(a, "flash prefill: chunk K/V hold fewer than M rows");
-        if (int r = encode_qkv_map(a, &tk1, *k1, n_kv, 1, bn, "k_chunk")) return r;
-        if (int r = encode_qkv_map(a, &tv1, *v1, n_kv, 1, bn, "v_chunk")) return r;
+        if (int r = encode_qkv_map(a, &tk1, *k1, n_kv, 1, BLOCK_N, "k_chunk")) return r;
+        if (int r = encode_qkv_map(a, &tv1, *v1, n_kv, 1, BLOCK_N, "v_chunk")) return r;
     } else {
         tk1 = tk0;
         tv1 = tv0;
     }
-    typedef void (*FlashKernel)(const CUtensorMap, const CUtensorMap, const CUtensorMap, const CUtensorMap, const CUtensorMap,
-                                const FlashParams);
-    typedef void (*FlashPPKernel)(const CUtensorMap, const CUtensorMap, const CUtensorMap, const FlashParams);
-    const int pidx = poly == 0 ? 0 : poly == 4 ? 1 : 2;
-    const int variant = pp ? 4 + pidx : bn == 64 ? 0 : 1 + pidx;
-    const FlashKernel kern = variant == 0   ? (FlashKernel)flash_prefill_kernel<TWO_SRC>
-                             : variant == 1 ? (FlashKernel)flash128_prefill_kernel<TWO_SRC, 0>
-                             : variant == 2 ? (FlashKernel)flash128_prefill_kernel<TWO_SRC, 4>
-                                            : (FlashKernel)flash128_prefill_kernel<TWO_SRC, 8>;
-    const FlashPPKernel kern_pp = pidx == 0 ? flash_pp_kernel<0> : pidx == 1 ? flash_pp_kernel<4> : flash_pp_kernel<8>;
-    const size_t smem = pp ? sizeof(FlashPPSmem) : bn == 64 ? sizeof(FlashSmem) : sizeof(Flash128Smem);
+    const size_t smem = sizeof(FlashSmem);
     {
         static std::mutex attr_mutex;
-        static bool attr_set[2][8][64] = {};
+        static bool attr_set[2][64] = {};
         std::lock_guard<std::mutex> lock(attr_mutex);
-        if (a.device < 64 && !attr_set[TWO_SRC][variant][a.device]) {
-            if (int r = check_cuda(a, cudaFuncSetAttribute(pp ? (const void*)kern_pp : (const void*)kern,
-                                                           cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem),
+        if (a.device < 64 && !attr_set[TWO_SRC][a.device]) {
+            if (int r = check_cuda(a, cudaFuncSetAttribute(flash_prefill_kernel<TWO_SRC>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem),
                                    "cudaFuncSetAttribute(flash_prefill)"))
                 return r;
-            attr_set[TWO_SRC][variant][a.device] = true;
+            attr_set[TWO_SRC][a.device] = true;
         }
     }
-    const uint32_t tok_per_cta = pp ? PP_TOK : BLOCK_TOK;
-    const uint32_t q_tiles = (m_tokens + tok_per_cta - 1) / tok_per_cta;
+    const size_t k_rows = k0.bytes / ((size_t)n_kv * HD * 2);
+    const uint32_t q_tiles = (m_tokens + BLOCK_TOK - 1) / BLOCK_TOK;
     const size_t rows = (size_t)m_tokens * n_q;
-    int pieces = TWO_SRC ? 1 : choose_pieces((size_t)q_tiles * n_kv, (pp ? 1 : 2) * a.sm_count, k0.bytes / ((size_t)n_kv * HD * 2), bn);
+    int pieces = TWO_SRC ? 1 : choose_pieces((size_t)q_tiles * n_kv, 2 * a.sm_count, k_rows);
     float* part_acc = nullptr;
     float* part_ml = nullptr;
     if (pieces > 1) {
@@ -1350,10 +604,7 @@ int run_flash(const LaunchArgs& a, const BufView& q, const BufView& k0, const Bu
     }
     FlashParams prm{(const uint32_t*)step.ptr, (float*)out.ptr, part_acc, part_ml, a.status, m_tokens, n_kv, window, ring, scale};
     const dim3 grid(q_tiles, n_kv, pieces);
-    if (pp)
-        kern_pp<<<grid, PP_THREADS, smem, a.stream>>>(tq, tk0, tv0, prm);
-    else
-        kern<<<grid, FLASH_THREADS, smem, a.stream>>>(tq, tk0, tv0, tk1, tv1, prm);
+    flash_prefill_kernel<TWO_SRC><<<grid, FLASH_THREADS, smem, a.stream>>>(tq, tk0, tv0, tk1, tv1, prm);
     ++*a.launches;
     if (int r = check_cuda(a, cudaGetLastError(), "attn_prefill_flash")) return r;
     if (pieces > 1) {
@@ -1397,10 +648,3 @@ int launch_prefill_paged_q8kv_flash_d128(const LaunchArgs& a)
 }
 
 }  // namespace sgb
-
-#ifdef SGB_FLASH_STAMPS
-extern "C" int sgb_debug_flash_stamps(unsigned long long* out)
-{
-    return (int)cudaMemcpyFromSymbol(out, sgb::g_flash_stamps, sizeof(unsigned long long) * 64);
-}
-#endif

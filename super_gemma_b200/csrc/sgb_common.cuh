@@ -160,15 +160,6 @@ __device__ __forceinline__ void tmem_ld_32x32b_x32(uint32_t taddr, uint32_t (&r)
         : "r"(taddr)
         : "memory");
 }
-__device__ __forceinline__ void tmem_st_32x32b_x16(uint32_t taddr, const uint32_t (&r)[16])
-{
-    asm volatile(
-        "tcgen05.st.sync.aligned.32x32b.x16.b32 [%0], "
-        "{%1, %2, %3, %4, %5, %6, %7, %8, %9, %10, %11, %12, %13, %14, %15, %16};"
-        ::"r"(taddr), "r"(r[0]), "r"(r[1]), "r"(r[2]), "r"(r[3]), "r"(r[4]), "r"(r[5]), "r"(r[6]), "r"(r[7]), "r"(r[8]),
-          "r"(r[9]), "r"(r[10]), "r"(r[11]), "r"(r[12]), "r"(r[13]), "r"(r[14]), "r"(r[15])
-        : "memory");
-}
 __device__ __forceinline__ void tmem_st_32x32b_x32(uint32_t taddr, const uint32_t (&r)[32])
 {
     asm volatile(
@@ -218,28 +209,17 @@ __device__ __forceinline__ float ex2(float x)
     asm("ex2.approx.ftz.f32 %0, %1;" : "=f"(y) : "f"(x));
     return y;
 }
-// 2^x for a pair on the FMA pipe instead of the special-function unit: x = n + f with n = round(x) taken
-// from the low mantissa bits of x + 1.5 * 2^23, 2^f by a cubic on [-0.5, 0.5] (relative error 7.7e-5), n added
-// into the exponent field.  For x <= 127; inputs below -126 (masked scores are -inf) give 2^-126.
-__device__ __forceinline__ float2 ex2_poly2(float2 x)
-{
-    x.x = fmaxf(x.x, -126.0f);
-    x.y = fmaxf(x.y, -126.0f);
-    const float2 t = __fadd2_rn(x, make_float2(12582912.0f, 12582912.0f));
-    const float2 n = __fadd2_rn(t, make_float2(-12582912.0f, -12582912.0f));
-    const float2 f = __ffma2_rn(n, make_float2(-1.0f, -1.0f), x);
-    float2 p = __ffma2_rn(f, make_float2(0.05508868396282196f, 0.05508868396282196f), make_float2(0.24260404706001282f, 0.24260404706001282f));
-    p = __ffma2_rn(p, f, make_float2(0.6932762265205383f, 0.6932762265205383f));
-    p = __ffma2_rn(p, f, make_float2(0.9999289512634277f, 0.9999289512634277f));
-    return make_float2(__int_as_float(__float_as_int(p.x) + (__float_as_int(t.x) << 23)),
-                       __int_as_float(__float_as_int(p.y) + (__float_as_int(t.y) << 23)));
-}
 // Programmatic dependent launch: a kernel launched with the stream-serialization attribute may start while its
 // predecessor in the stream still runs; it must call pdl_wait() before it touches anything the predecessor
 // (or anything earlier in the stream) wrote.  pdl_launch_dependents() lets the successor's CTAs be scheduled as
 // soon as every CTA of this grid has called it.  Both are no-ops for a plain launch.
 __device__ __forceinline__ void pdl_wait() { asm volatile("griddepcontrol.wait;" ::: "memory"); }
 __device__ __forceinline__ void pdl_launch_dependents() { asm volatile("griddepcontrol.launch_dependents;" ::: "memory"); }
+// Barrier `id` (1..15; 0 is __syncthreads) over `threads` threads of the CTA, a multiple of 32.
+__device__ __forceinline__ void named_barrier_sync(uint32_t id, uint32_t threads)
+{
+    asm volatile("bar.sync %0, %1;" ::"r"(id), "r"(threads) : "memory");
+}
 // Three-input maximum (one instruction on sm_100).
 __device__ __forceinline__ float max3(float a, float b, float c)
 {
