@@ -394,18 +394,21 @@ def prefill_output(dev, kvh, m, ctx_len, seed):
 
 def check_sharded_prefill(dev, rank, world, dist, m=512, ctx_len=8192, seed=0x5607):
     """Every rank computes its kv-head slice the way the sharded run does, and the same heads inside a launch over
-    all 16 kv heads the way a 1-GPU run does; the two must agree (the launch geometry may cut the key range into a
-    different number of pieces, so agreement is to rounding, not to the bit)."""
+    all 16 kv heads the way a 1-GPU run does; the two must agree within the parity tolerance (the launch geometry may
+    cut the key range into a different number of pieces, each with its own running maximum, so P is rounded to f16 at
+    different scales and the bits differ)."""
     torch = dev.torch
     mine = list(range(rank * KV // world, (rank + 1) * KV // world))
     a = prefill_output(dev, mine, m, ctx_len, seed)
     b = prefill_output(dev, list(range(KV)), m, ctx_len, seed)[:, mine[0] * G:(mine[-1] + 1) * G]
     diff = float((a - b).abs().max().item())
-    ok = torch.tensor([1 if (diff <= 2e-5 and bool(torch.isfinite(a).all())) else 0], device=dev.device)
+    within = bool(((a - b).abs() <= 2e-3 + 1e-2 * b.abs()).all()) and bool(torch.isfinite(a).all())
+    ok = torch.tensor([1 if within else 0], device=dev.device)
     worst = torch.tensor([diff], dtype=torch.float64, device=dev.device)
     dist.all_reduce(ok, op=dist.ReduceOp.MIN)
     dist.all_reduce(worst, op=dist.ReduceOp.MAX)
-    return {"agrees": bool(ok.item() == 1), "max_abs_diff": float(worst.item()), "shape": f"{m} queries over {ctx_len} tokens, every rank"}
+    return {"agrees": bool(ok.item() == 1), "max_abs_diff": float(worst.item()), "tolerance": "2e-3 + 1e-2*|x|",
+            "shape": f"{m} queries over {ctx_len} tokens, every rank"}
 
 
 def run_decode(dev, rank, world, steps, warmup, dist, ctx_len, m_q, n_splits, seed, copies=4):
@@ -455,43 +458,19 @@ def run_decode(dev, rank, world, steps, warmup, dist, ctx_len, m_q, n_splits, se
             dist.all_gather_into_tensor(gathered, mine)
         dev.ctx.dispatch(comb, dev.bind(b_gath, b_out), world, [rows, 1, 1])
 
-    tickets = torch.zeros(KV, dtype=torch.int32, device=dev.device)
-    b_tick = W(tickets)
-    decf, decx = dev.kernel("attn_decode_paged_q8kv_fused_d128"), dev.kernel("attn_decode_paged_q8kv_xchg_d128")
-
-    def step_one_launch(timer, base):  # decode + combine (+ exchange) in ONE kernel
-        kq, ks, vq, vs, tab = b_pools[base % len(b_pools)]
-        if timer is not None:
-            timer.stamp(base)
-        if world == 1:
-            dev.ctx.dispatch(decf, dev.bind(b_q, kq, ks, vq, vs, tab, b_part, b_tick, b_out, b_step), (n_splits, SCALE, PAGE), [KV, n_splits, m_q])
-        else:
-            dev.ctx.dispatch(decx, dev.bind(b_q, kq, ks, vq, vs, tab, b_part, b_tick, b_x, b_peers, b_out, b_step),
-                             (n_splits, SCALE, PAGE, world, rank, 0), [KV, n_splits, m_q])
-
     tail0 = tail_local if world == 1 else tail_nccl
     kv_bytes = ctx_len * KV * (D + 8) * 2  # quants + scales, K and V
     algo = kv_bytes + m_q * H * D * 2 + m_q * H * D * 4 + (ctx_len // PAGE) * 4
-    # the decode kernel alone (a stamp between the two kernels), then the whole step with nothing between them
+    # the decode kernel alone (a stamp between the two kernels), then the whole step with nothing between its kernels
     _, deltas, _ = timed(dev, make_step(True, tail0), steps, warmup, dist, stamps_per_step=2, graph=(world == 1))
-    total_2, _, _ = timed(dev, make_step(False, tail0), steps, warmup, dist, stamps_per_step=0, graph=(world == 1))
+    total_s, _, launches = timed(dev, make_step(False, tail0), steps, warmup, dist, stamps_per_step=0, graph=(world == 1))
     kern_us = float(np.median(deltas[:, 0])) * 1e-3
-    res = {"kernel_us": kern_us, "kernel_gbs": (algo / world) / kern_us / 1e3, "algorithmic_bytes": algo, "n_splits": n_splits}
-    if world == 1:
-        total_s, _, launches = timed(dev, step_one_launch, steps, warmup, dist, stamps_per_step=0, graph=True)
-        res.update({"us_per_step": total_s / steps * 1e6, "gbs": algo * steps / total_s / 1e9, "launches": launches,
-                    "two_kernel_us_per_step": total_2 / steps * 1e6,
-                    "step": "attn_decode_paged_q8kv_fused_d128 (decode + combine in one launch); two_kernel_* = decode, then attn_reduce_f32_d128"})
-        # correctness of what was just timed: same pool through both forms, bit for bit
-        make_step(False, tail_local)(None, 0)
-        dev.ctx.sync()
-        ref = out.clone()
-        out.zero_()
-        step_one_launch(None, 0)
-        dev.ctx.sync()
-        res["fused_agrees"] = bool(torch.equal(ref.view(torch.int32), out.view(torch.int32))) and bool(torch.isfinite(out).all())
-    else:
-        res.update({"nccl_us_per_step": total_2 / steps * 1e6, "nccl_gbs": algo * steps / total_2 / 1e9})
+    res = {"us_per_step": total_s / steps * 1e6, "gbs": algo * steps / total_s / 1e9, "kernel_us": kern_us,
+           "kernel_gbs": (algo / world) / kern_us / 1e3, "algorithmic_bytes": algo, "n_splits": n_splits, "launches": launches,
+           "step": "attn_decode_paged_q8kv_d128, then attn_reduce_f32_d128"}
+    if world > 1:
+        # The same step with the combine and the exchange in ONE kernel over peer memory (attn_reduce_exchange_d128)
+        # instead of reduce + NCCL all-gather + combine; no collective call, so it replays as a CUDA graph.
         try:
             from super_gemma_b200 import sharding
 
@@ -502,21 +481,20 @@ def run_decode(dev, rank, world, steps, warmup, dist, ctx_len, m_q, n_splits, se
             def tail_fused():
                 dev.ctx.dispatch(fx, dev.bind(b_part, b_x, b_peers, b_out), (n_splits, world, rank, 0), [rows, 1, 1])
 
-            total_f, _, _ = timed(dev, make_step(False, tail_fused), steps, warmup, dist, stamps_per_step=0, graph=True)
-            total_s, _, launches = timed(dev, step_one_launch, steps, warmup, dist, stamps_per_step=0, graph=True)
-            res.update({"us_per_step": total_s / steps * 1e6, "gbs": algo * steps / total_s / 1e9, "launches": launches,
-                        "two_launch_us_per_step": total_f / steps * 1e6,
-                        "step": f"attn_decode_paged_q8kv_xchg_d128: decode, combine and exchange over NVLink peer stores ({keep[1]}) in one launch; "
-                                "two_launch_* = decode, then attn_reduce_exchange_d128; nccl_* = decode, reduce, all-gather, combine"})
-            # Correctness of what was just timed: the same pool through all three forms, compared bit for bit on every rank.
+            total_f, _, launches_f = timed(dev, make_step(False, tail_fused), steps, warmup, dist, stamps_per_step=0, graph=True)
+            res.update({"nccl_us_per_step": res["us_per_step"], "nccl_gbs": res["gbs"], "us_per_step": total_f / steps * 1e6,
+                        "gbs": algo * steps / total_f / 1e9, "launches": launches_f,
+                        "step": f"attn_decode_paged_q8kv_d128, then attn_reduce_exchange_d128 (combine + exchange over NVLink peer stores, "
+                                f"{keep[1]}); nccl_* = decode, reduce, NCCL all-gather, combine"})
+            # Correctness of what was just timed: the same pool through both forms, compared bit for bit on every rank.
             outs = []
-            for form in (make_step(False, tail_nccl), make_step(False, tail_fused), step_one_launch):
+            for form in (make_step(False, tail_nccl), make_step(False, tail_fused)):
                 out.zero_()
                 form(None, 0)
                 dev.ctx.sync()
                 dist.barrier()
                 outs.append(out.clone())
-            same = all(bool(torch.equal(outs[0].view(torch.int32), o.view(torch.int32))) for o in outs[1:]) and bool(torch.isfinite(outs[2]).all())
+            same = bool(torch.equal(outs[0].view(torch.int32), outs[1].view(torch.int32))) and bool(torch.isfinite(outs[1]).all())
             flag = torch.tensor([1 if same else 0], device=dev.device)
             dist.all_reduce(flag, op=dist.ReduceOp.MIN)
             res["exchange_agrees"] = bool(flag.item() == 1)
@@ -567,13 +545,12 @@ def run_decode_block(dev, steps, warmup, ctx_len, n_splits, seed, chunk=4096):
     out = torch.zeros(H * D, dtype=torch.float32, device=dev.device)
     step_t = torch.tensor([ctx_len - 1, 0, ctx_len, 0], dtype=torch.int32, device=dev.device)  # the token lands in the last row
     k1, v1 = k_raw[:1].contiguous(), v_raw[:1].contiguous()
-    tickets = torch.zeros(KV, dtype=torch.int32, device=dev.device)
     torch.cuda.synchronize()
     W = dev.wrap
-    b = {n: W(t) for n, t in dict(q_raw=q_raw, k1=k1, v1=v1, q_w=q_w, k_w=k_w, cs=cos_sin, q=q, part=part, out=out, step=step_t, tickets=tickets, kq=kq, ks=ks,
+    b = {n: W(t) for n, t in dict(q_raw=q_raw, k1=k1, v1=v1, q_w=q_w, k_w=k_w, cs=cos_sin, q=q, part=part, out=out, step=step_t, kq=kq, ks=ks,
                                   vq=vq, vs=vs, table=table).items()}
     qkv, fused = dev.kernel("qkv_norm_rope_append_paged_q8_d128"), dev.kernel("kv_norm_rope_append_paged_q8_d128")
-    dec = dev.kernel("attn_decode_paged_q8kv_fused_d128")
+    dec, red = dev.kernel("attn_decode_paged_q8kv_d128"), dev.kernel("attn_reduce_f32_d128")
     row = KV * D
 
     def step(timer, base):
@@ -581,11 +558,12 @@ def run_decode_block(dev, steps, warmup, ctx_len, n_splits, seed, chunk=4096):
             timer.stamp(base)
         dev.ctx.dispatch(qkv, dev.bind(b["q_raw"], b["q_w"], b["q"], b["k1"], b["v1"], b["k_w"], b["cs"], b["ks"], b["kq"], b["vs"], b["vq"],
                                        b["table"], b["step"]), (H, row, PAGE, D, 0), [1, 1, 1])
-        dev.ctx.dispatch(dec, dev.bind(b["q"], b["kq"], b["ks"], b["vq"], b["vs"], b["table"], b["part"], b["tickets"], b["out"], b["step"]),
-                         (n_splits, SCALE, PAGE), [KV, n_splits, 1])
+        dev.ctx.dispatch(dec, dev.bind(b["q"], b["kq"], b["ks"], b["vq"], b["vs"], b["table"], b["part"], b["step"]), (n_splits, SCALE, PAGE),
+                         [KV, n_splits, 1])
+        dev.ctx.dispatch(red, dev.bind(b["part"], b["out"]), n_splits, [H, 1, 1])
 
     total_s, _, launches = timed(dev, step, steps, warmup, None, stamps_per_step=0, graph=True)
-    res = {"us_per_token": total_s / steps * 1e6, "launches": launches, "kernels_per_token": 2, "ctx": ctx_len, "n_splits": n_splits,
+    res = {"us_per_token": total_s / steps * 1e6, "launches": launches, "kernels_per_token": 3, "ctx": ctx_len, "n_splits": n_splits,
            "note": "one cache copy: parts of the 143 MB stream may be served from the 126 MB L2"}
     # the fused append alone, on a prefill chunk written at positions 0..chunk-1
     step0 = torch.zeros(4, dtype=torch.int32, device=dev.device)

@@ -34,7 +34,6 @@
 #include <mutex>
 #include <string>
 
-#include "attn_exchange.cuh"
 #include "attn_merge.cuh"
 #include "sgb_common.cuh"
 #include "sgb_kernels.h"
@@ -121,31 +120,13 @@ __device__ __forceinline__ float quad_sum(float v)
     return v + __shfl_xor_sync(0xffffffffu, v, 2);
 }
 
-// What the kernel does after its partials are written.
-//   MODE 0  nothing: the caller runs attn_reduce_* (the reference's two-kernel shape).
-//   MODE 1  the combine, folded in: every CTA draws a ticket per kv head it holds; the CTA that draws a head's last
-//           ticket merges all splits of that head's rows in index order (merge_splits_running, the arithmetic of
-//           attn_reduce_f32_d128) and writes out.  Nobody waits, and the bits do not depend on who merges.
-//   MODE 2  the combine and the exchange between the ranks of a sequence-parallel decode: the merging CTA hands each
-//           merged row to every rank over NVLink and merges the ranks' rows (exchange_row, the arithmetic of
-//           attn_reduce_exchange_d128).  The waiting CTA is the last of its head on this GPU and waits only for the
-//           same head's last CTA on the other GPUs, so no wait depends on work that has not been scheduled.
-struct DecodeTail {
-    float* out;                        // f32 [m_q x H x 128]
-    uint32_t* tickets;                 // u32 [kv heads], zero before the first launch; the last CTA of a head re-zeroes its word
-    float* xbuf;                       // MODE 2: this rank's exchange buffer
-    const unsigned long long* peers;   // MODE 2: every rank's exchange buffer, rank order
-    uint32_t world, rank;
-    long long wait_cycles;
-};
-
-template <int NSTAGES, int MIN_CTAS, int SUB, int MODE>
+template <int NSTAGES, int MIN_CTAS, int SUB>
 __global__ void __launch_bounds__(WPC * 32, MIN_CTAS)
     decode_paged_kernel(const __grid_constant__ CUtensorMap tm_kq, const __grid_constant__ CUtensorMap tm_ks,
                         const __grid_constant__ CUtensorMap tm_vq, const __grid_constant__ CUtensorMap tm_vs,
                         const __half* __restrict__ q, const uint32_t* __restrict__ page_table, uint32_t table_len, uint32_t page,
                         uint32_t pool_pages, float* __restrict__ part, const uint32_t* __restrict__ step, uint32_t n_kv,
-                        uint32_t n_splits, float scale, uint32_t m_q, uint32_t* status, const DecodeTail tail)
+                        uint32_t n_splits, float scale, uint32_t m_q, uint32_t* status)
 {
     extern __shared__ uint8_t smem_raw[];
     using Smem = DecodeSmem<NSTAGES>;
@@ -477,45 +458,6 @@ __global__ void __launch_bounds__(WPC * 32, MIN_CTAS)
             }
         }
     }
-
-    // ---- the combine (and the exchange), by the CTA that finishes a head last -------------------------------
-    if constexpr (MODE != 0) {
-        __shared__ uint32_t s_last[WPC];
-        __shared__ uint32_t s_timed_out[2];
-        __threadfence();  // this thread's partial stores are visible device-wide before the ticket is drawn
-        __syncthreads();
-        if (threadIdx.x < HEADS_PER_CTA) {
-            const int h = blockIdx.x * HEADS_PER_CTA + threadIdx.x;
-            uint32_t last = 0;
-            if (h < (int)n_kv) {
-                last = atomicAdd(tail.tickets + h, 1u) == n_splits - 1 ? 1u : 0u;
-                if (last) tail.tickets[h] = 0;  // every CTA that holds this head has drawn: ready for the next launch
-            }
-            s_last[threadIdx.x] = last;
-        }
-        if (threadIdx.x < 2) s_timed_out[threadIdx.x] = 0;
-        __syncthreads();
-        const int grp = warp >> 1, tg = threadIdx.x & 63;  // two groups of 64 threads, one row each, two dims per thread
-#pragma unroll 1
-        for (int hl = 0; hl < HEADS_PER_CTA; hl++) {
-            if (!s_last[hl]) continue;  // uniform over the CTA
-            __threadfence();
-            const int h = blockIdx.x * HEADS_PER_CTA + hl;
-#pragma unroll 1
-            for (uint32_t rp = 0; rp < rows; rp += 2) {  // the head's m_q * G rows, two at a time (G = 2: an even count)
-                const uint32_t r = rp + grp;
-                const size_t row = (size_t)(r / G) * n_q + h * G + r % G;
-                float acc[2];
-                const MergeState st = merge_splits_running<HD, 2>(part + row * n_splits * (HD + 2), HD + 2, n_splits, 2 * tg, acc);
-                if constexpr (MODE == 1) {
-                    *reinterpret_cast<float2*>(tail.out + row * HD + 2 * tg) = make_float2(acc[0] / st.l, acc[1] / st.l);
-                } else {
-                    exchange_row(acc, st, row, (size_t)m_q * n_q, tg, 1 + grp, &s_timed_out[grp], tail.xbuf, tail.peers, tail.world,
-                                 tail.rank, tail.wait_cycles, status, tail.out, nullptr);
-                }
-            }
-        }
-    }
 }
 
 struct PushDecodePaged {
@@ -542,11 +484,10 @@ int encode_pool_maps(const LaunchArgs& a, CUtensorMap (&tm)[4], const void* cons
     return 0;
 }
 
-template <int NSTAGES, int MIN_CTAS, int SUB, int MODE>
+template <int NSTAGES, int MIN_CTAS, int SUB>
 cudaError_t launch_decode_variant(cudaStream_t stream, int device, const CUtensorMap (&tm)[4], const __half* q,
                                   const uint32_t* page_table, uint32_t table_len, uint32_t page, uint32_t pool_pages, float* part,
-                                  const uint32_t* step, uint32_t n_kv, uint32_t n_splits, float scale, uint32_t m_q, uint32_t* status,
-                                  const DecodeTail& tail)
+                                  const uint32_t* step, uint32_t n_kv, uint32_t n_splits, float scale, uint32_t m_q, uint32_t* status)
 {
     using Smem = DecodeSmem<NSTAGES>;
     const size_t smem = sizeof(Smem) + 1024;
@@ -555,16 +496,15 @@ cudaError_t launch_decode_variant(cudaStream_t stream, int device, const CUtenso
     {
         std::lock_guard<std::mutex> lock(attr_mutex);
         if (device >= 0 && device < 64 && !attr_set[device]) {
-            cudaError_t e = cudaFuncSetAttribute(decode_paged_kernel<NSTAGES, MIN_CTAS, SUB, MODE>,
+            cudaError_t e = cudaFuncSetAttribute(decode_paged_kernel<NSTAGES, MIN_CTAS, SUB>,
                                                  cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
             if (e != cudaSuccess) return e;
             attr_set[device] = true;
         }
     }
     const uint32_t ctas_x = (n_kv * SUB + WPC - 1) / WPC;
-    return launch_dependent(decode_paged_kernel<NSTAGES, MIN_CTAS, SUB, MODE>, dim3(ctas_x, n_splits), dim3(WPC * 32), smem, stream, tm[0],
-                            tm[1], tm[2], tm[3], q, page_table, table_len, page, pool_pages, part, step, n_kv, n_splits, scale, m_q, status,
-                            tail);
+    return launch_dependent(decode_paged_kernel<NSTAGES, MIN_CTAS, SUB>, dim3(ctas_x, n_splits), dim3(WPC * 32), smem, stream, tm[0],
+                            tm[1], tm[2], tm[3], q, page_table, table_len, page, pool_pages, part, step, n_kv, n_splits, scale, m_q, status);
 }
 
 // Shape of the launch.  Three 4.5 KB stages per warp = 54 KB per CTA and 128 registers per thread let
@@ -572,11 +512,9 @@ cudaError_t launch_decode_variant(cudaStream_t stream, int device, const CUtenso
 // of 4, 2, 1 for which all warps still fit on the GPU at once (one wave): extra waves cost more
 // than the parallelism buys.  SGB_DECODE_SUB=1|2|4 overrides the choice (tuning aid; results agree
 // within rounding, each choice is bit-reproducible).
-template <int MODE>
 cudaError_t launch_decode(cudaStream_t stream, int device, int sm_count, const CUtensorMap (&tm)[4], const __half* q,
                           const uint32_t* page_table, uint32_t table_len, uint32_t page, uint32_t pool_pages, float* part,
-                          const uint32_t* step, uint32_t n_kv, uint32_t n_splits, float scale, uint32_t m_q, uint32_t* status,
-                          const DecodeTail& tail = DecodeTail{})
+                          const uint32_t* step, uint32_t n_kv, uint32_t n_splits, float scale, uint32_t m_q, uint32_t* status)
 {
     static const int forced = [] {
         const char* e = getenv("SGB_DECODE_SUB");
@@ -586,26 +524,22 @@ cudaError_t launch_decode(cudaStream_t stream, int device, int sm_count, const C
     const uint64_t tasks = (uint64_t)n_kv * n_splits;
     int sub = tasks * 4 <= slots ? 4 : tasks * 2 <= slots ? 2 : 1;
     if (forced == 1 || forced == 2 || forced == 4) sub = forced;
-#define SGB_DECODE_ARGS stream, device, tm, q, page_table, table_len, page, pool_pages, part, step, n_kv, n_splits, scale, m_q, status, tail
-    if (sub == 4) return launch_decode_variant<3, 4, 4, MODE>(SGB_DECODE_ARGS);
-    if (sub == 2) return launch_decode_variant<3, 4, 2, MODE>(SGB_DECODE_ARGS);
-    return launch_decode_variant<3, 4, 1, MODE>(SGB_DECODE_ARGS);
+#define SGB_DECODE_ARGS stream, device, tm, q, page_table, table_len, page, pool_pages, part, step, n_kv, n_splits, scale, m_q, status
+    if (sub == 4) return launch_decode_variant<3, 4, 4>(SGB_DECODE_ARGS);
+    if (sub == 2) return launch_decode_variant<3, 4, 2>(SGB_DECODE_ARGS);
+    return launch_decode_variant<3, 4, 1>(SGB_DECODE_ARGS);
 #undef SGB_DECODE_ARGS
 }
 
-struct PushDecodeXchg {
-    uint32_t n_splits;
-    float scale;
-    uint32_t page;
-    uint32_t world, rank;
-    uint32_t wait_us;  // limit of the wait for the peers in microseconds; 0 = about a second
-};
+}  // namespace
 
-// Shared by the three registry forms.  Bindings 0..6 are always q, k_quants, k_scales, v_quants, v_scales, page_table,
-// part; `tail_at` is the index of the first binding after them, `step_at` the index of the step buffer.
-template <int MODE>
-int run_decode_paged(const LaunchArgs& a, const PushDecodeXchg& p, int tail_at, int step_at)
+// attn_decode_paged_q8kv_d128 / attn_verify_paged_q8kv_d128.
+// bindings: q f16 [m_q x H x 128], k_quants i8, k_scales f16, v_quants i8, v_scales f16,
+//           page_table u32, part f32 [m_q*H x n_splits x 130], step.
+// push {n_splits u32, scale f32, page u32}.  grid [n_kv_heads, n_splits, m_q (0 or 1 = decode)].
+int launch_decode_paged_q8kv_d128(const LaunchArgs& a)
 {
+    const PushDecodePaged p = *(const PushDecodePaged*)a.push;
     const uint32_t n_kv = a.groups[0];
     const uint32_t m_q = a.groups[2] ? a.groups[2] : 1;
     if (n_kv == 0 || (n_kv & 1)) return fail_validation(a, "decode_paged: groups[0] (kv heads) must be even and > 0");
@@ -621,67 +555,22 @@ int run_decode_paged(const LaunchArgs& a, const PushDecodeXchg& p, int tail_at, 
     if (a.b[2].bytes / 2 < pool_rows * n_kv * 4 || a.b[4].bytes / 2 < pool_rows * n_kv * 4)
         return fail_validation(a, "decode_paged: scales pool too short for its quants pool");
     if (a.b[5].bytes < 4) return fail_validation(a, "decode_paged: empty page table");
-    const size_t n_q = (size_t)n_kv * G, rows = m_q * n_q;
-    if (a.b[0].bytes < rows * HD * 2) return fail_validation(a, "decode_paged: q buffer too small");
-    if (int r = need_bytes(a, 6, rows * p.n_splits * (HD + 2) * 4, "part")) return r;
-    if (int r = need_bytes(a, step_at, 16, "step")) return r;
+    const size_t n_q = (size_t)n_kv * G;
+    if (a.b[0].bytes < m_q * n_q * HD * 2) return fail_validation(a, "decode_paged: q buffer too small");
+    if (int r = need_bytes(a, 6, m_q * n_q * p.n_splits * (HD + 2) * 4, "part")) return r;
+    if (int r = need_bytes(a, 7, 16, "step")) return r;
     for (int i = 1; i <= 4; i++)
         if (reinterpret_cast<uintptr_t>(a.b[i].ptr) & 15) return fail_validation(a, "decode_paged: K/V pools must be 16-byte aligned");
-    DecodeTail tail{};
-    if (MODE != 0) {
-        if (int r = need_bytes(a, tail_at, (size_t)n_kv * 4, "tickets")) return r;
-        tail.tickets = (uint32_t*)a.b[tail_at].ptr;
-        int at = tail_at + 1;
-        if (MODE == 2) {
-            if (p.world == 0 || p.world > 64 || p.rank >= p.world) return fail_validation(a, "decode_paged_xchg: world in 1..64 and rank < world");
-            if (int r = need_bytes(a, at, xchg_words(p.world, rows) * 4, "exchange buffer")) return r;
-            if (int r = need_bytes(a, at + 1, (size_t)p.world * 8, "peers")) return r;
-            tail.xbuf = (float*)a.b[at].ptr;
-            tail.peers = (const unsigned long long*)a.b[at + 1].ptr;
-            tail.world = p.world;
-            tail.rank = p.rank;
-            tail.wait_cycles = (long long)p.wait_us * 2000;  // 2 cycles per nanosecond bounds the SM clock from above
-            at += 2;
-        }
-        if (int r = need_bytes(a, at, rows * HD * 4, "out")) return r;
-        tail.out = (float*)a.b[at].ptr;
-    }
+
     CUtensorMap tm[4];
     const void* const quants[2] = {a.b[1].ptr, a.b[3].ptr};
     const void* const scales[2] = {a.b[2].ptr, a.b[4].ptr};
     if (int r = encode_pool_maps(a, tm, quants, scales, n_kv, pool_rows)) return r;
-    const cudaError_t e = launch_decode<MODE>(a.stream, a.device, a.sm_count, tm, (const __half*)a.b[0].ptr, (const uint32_t*)a.b[5].ptr,
-                                              (uint32_t)(a.b[5].bytes / 4), p.page, (uint32_t)(pool_rows / p.page), (float*)a.b[6].ptr,
-                                              (const uint32_t*)a.b[step_at].ptr, n_kv, p.n_splits, p.scale, m_q, a.status, tail);
+    const cudaError_t e = launch_decode(a.stream, a.device, a.sm_count, tm, (const __half*)a.b[0].ptr, (const uint32_t*)a.b[5].ptr,
+                                        (uint32_t)(a.b[5].bytes / 4), p.page, (uint32_t)(pool_rows / p.page), (float*)a.b[6].ptr,
+                                        (const uint32_t*)a.b[7].ptr, n_kv, p.n_splits, p.scale, m_q, a.status);
     ++*a.launches;
     return check_cuda(a, e, "attn_decode_paged_q8kv_d128");
-}
-
-}  // namespace
-
-// attn_decode_paged_q8kv_d128 / attn_verify_paged_q8kv_d128.
-// bindings: q f16 [m_q x H x 128], k_quants i8, k_scales f16, v_quants i8, v_scales f16,
-//           page_table u32, part f32 [m_q*H x n_splits x 130], step.
-// push {n_splits u32, scale f32, page u32}.  grid [n_kv_heads, n_splits, m_q (0 or 1 = decode)].
-int launch_decode_paged_q8kv_d128(const LaunchArgs& a)
-{
-    const PushDecodePaged p = *(const PushDecodePaged*)a.push;
-    return run_decode_paged<0>(a, PushDecodeXchg{p.n_splits, p.scale, p.page, 1, 0, 0}, 7, 7);
-}
-
-// attn_decode_paged_q8kv_fused_d128: decode + combine in one launch.
-// bindings: the first seven of attn_decode_paged_q8kv_d128, then tickets u32[kv heads] (zeroed once), out f32 [m_q*H x 128], step.
-int launch_decode_paged_q8kv_fused_d128(const LaunchArgs& a)
-{
-    const PushDecodePaged p = *(const PushDecodePaged*)a.push;
-    return run_decode_paged<1>(a, PushDecodeXchg{p.n_splits, p.scale, p.page, 1, 0, 0}, 7, 9);
-}
-
-// attn_decode_paged_q8kv_xchg_d128: decode + combine + exchange between the ranks of a sequence-parallel decode.
-// bindings: the first seven, then tickets, xbuf, peers, out, step.  push {n_splits, scale, page, world, rank, wait_us}.
-int launch_decode_paged_q8kv_xchg_d128(const LaunchArgs& a)
-{
-    return run_decode_paged<2>(a, *(const PushDecodeXchg*)a.push, 7, 11);
 }
 
 }  // namespace sgb
@@ -728,7 +617,7 @@ __global__ void __launch_bounds__(HD / 2) noalloc_reduce_kernel(float* __restric
     const size_t row = blockIdx.x;
     const int d0 = 2 * threadIdx.x;
     float acc[2];
-    const MergeState st = merge_splits_running<HD, 2>(g_noalloc_scratch + row * n_splits * (HD + 2), HD + 2, n_splits, d0, acc);
+    const MergeState st = merge_splits_running<HD, 2, 3>(g_noalloc_scratch + row * n_splits * (HD + 2), HD + 2, n_splits, d0, acc);
     *reinterpret_cast<float2*>(out + row * HD + d0) = make_float2(acc[0] / st.l, acc[1] / st.l);
 }
 
@@ -805,7 +694,7 @@ extern "C" int sgb_decode_paged_q8kv_d128_noalloc(int device, void* stream, cons
     noalloc_step_kernel<<<1, 1, 0, s>>>(kv_len);
     int sm_count = 0;
     cudaDeviceGetAttribute(&sm_count, cudaDevAttrMultiProcessorCount, device);
-    e = launch_decode<0>(s, device, sm_count, tm, (const __half*)q, page_table, table_len, page, (uint32_t)(pool_rows / page), scratch, step,
+    e = launch_decode(s, device, sm_count, tm, (const __half*)q, page_table, table_len, page, (uint32_t)(pool_rows / page), scratch, step,
                       n_kv_heads, n_splits, scale, m_q, status);
     if (e != cudaSuccess) return set_last_error(4, std::string("decode_noalloc: launch: ") + cudaGetErrorString(e));
     noalloc_reduce_kernel<<<m_q * n_kv_heads * G, HD / 2, 0, s>>>(out, n_splits);

@@ -4,16 +4,11 @@
 // (acc[128], m, l) per query row, the ranks exchange those 520-byte rows, and each merges all of them in
 // rank order (attn_reduce.wgsl:29-56 is the merge; the reference is single-GPU and has no exchange).  Done
 // as reduce + all-gather + combine that is three launches and a collective whose latency, not its 17 KB, sets
-// the step time.  attn_reduce_exchange_d128 does it in one launch over peer memory:
-//   1. merge the local splits of row r                                   (arithmetic of attn_reduce_partial_d128)
-//   2. store the merged row into slot [parity][my rank][r] of EVERY rank's exchange buffer with plain peer
-//      stores over NVLink, fence, then release-store the step's epoch into that slot's flag
-//   3. acquire-poll the local flags of all ranks for row r (bounded: about a second, then DEV_ERR_TIMEOUT)
-//   4. merge the ranks' rows in rank order and write out                 (arithmetic of attn_combine_ranks_d128)
-// One CTA per row, so a row depends only on the same row of the other ranks.  Slots alternate with the parity
-// of a per-row epoch kept in the buffer: a rank can be at most one step ahead of a peer that still reads the
-// other parity, because its next step needs that peer's row of the current one.  The buffer must be zeroed
-// once, before the first use and after all ranks have allocated it.  No multimem, no TMA: plain ld/st.
+// the step time.  attn_reduce_exchange_d128 does it in one launch over peer memory: one CTA of 64 threads per
+// row merges the row's local splits (arithmetic of attn_reduce_partial_d128) and hands the result to
+// exchange_row (attn_exchange.cuh), which stores it into every rank's buffer over NVLink, waits (bounded) for
+// the same row of all ranks and merges them in rank order (arithmetic of attn_combine_ranks_d128).  A row
+// depends only on the same row of the other ranks.
 #include "attn_exchange.cuh"
 #include "sgb_kernels.h"
 
@@ -24,7 +19,6 @@ namespace {
 constexpr int HD = XCHG_HD;
 constexpr int ROWF = XCHG_ROWF;
 constexpr int XCHG_MAX_SPLITS = 1024;
-constexpr int XCHG_MAX_RANKS = 64;
 
 // One CTA of 64 threads per row.  The wait limit is a launch argument (cycles of the SM clock) so that a host
 // whose ranks may launch far apart can raise it; 0 means the library's default of about a second.
@@ -43,7 +37,7 @@ __global__ void __launch_bounds__(HD / 2) reduce_exchange_kernel(const float* __
     __syncthreads();
     // the local splits of this row, ascending, running maximum
     float acc[2];
-    const MergeState st = merge_splits_running<HD, 2>(part + row * n_splits * ROWF, ROWF, n_splits, 2 * t, acc);
+    const MergeState st = merge_splits_running<HD, 2, 3>(part + row * n_splits * ROWF, ROWF, n_splits, 2 * t, acc);
     if (stamp) t_phase[1] = globaltimer_ns();
     exchange_row(acc, st, row, rows, t, 1, &timed_out, xbuf, peers, world, rank, wait_cycles, status, out, stamp ? t_phase + 2 : nullptr);
     if (stamp) {
@@ -64,7 +58,7 @@ int run_reduce_exchange(const LaunchArgs& a, bool timed)
     if (rows == 0 || p.n_splits == 0 || p.n_splits > (uint32_t)XCHG_MAX_SPLITS)
         return fail_validation(a, "attn_reduce_exchange_d128: groups[0] (rows) must be > 0 and n_splits in 1..1024");
     if (p.world == 0 || p.world > (uint32_t)XCHG_MAX_RANKS || p.rank >= p.world)
-        return fail_validation(a, "attn_reduce_exchange_d128: world in 1..64 and rank < world");
+        return fail_validation(a, "attn_reduce_exchange_d128: world in 1..32 and rank < world");
     if (int r = need_bytes(a, 0, rows * p.n_splits * ROWF * 4, "part")) return r;
     if (int r = need_bytes(a, 1, xchg_words(p.world, rows) * 4, "exchange buffer")) return r;
     if (int r = need_bytes(a, 2, (size_t)p.world * 8, "peers")) return r;

@@ -254,7 +254,7 @@ __global__ void __launch_bounds__(HD / 2) reduce_kernel(const float* __restrict_
     const size_t s_stride = split_major ? rows * (HD + 2) : (size_t)(HD + 2);
     const float* base = part + (split_major ? row : row * n_splits) * (HD + 2);
     float acc[2];
-    const MergeState st = merge_splits_running<HD, 2>(base, s_stride, n_splits, d0, acc);
+    const MergeState st = merge_splits_running<HD, 2, 3>(base, s_stride, n_splits, d0, acc);  // up to 96 splits in one latency
     if constexpr (OUT_MODE == 2) {
         float* o = reinterpret_cast<float*>(out) + row * (HD + 2);
         *reinterpret_cast<float2*>(o + d0) = make_float2(acc[0], acc[1]);

@@ -102,8 +102,6 @@ int launch_reduce_exchange_timed_d128(const LaunchArgs&);
 
 // attn_decode_paged.cu
 int launch_decode_paged_q8kv_d128(const LaunchArgs&);
-int launch_decode_paged_q8kv_fused_d128(const LaunchArgs&);
-int launch_decode_paged_q8kv_xchg_d128(const LaunchArgs&);
 
 // attn_prefill_flash.cu
 int launch_prefill_flash_f16_d128(const LaunchArgs&);

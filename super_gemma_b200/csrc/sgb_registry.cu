@@ -89,16 +89,6 @@ const KernelEntry REGISTRY[] = {
     {"attn_verify_paged_q8kv_d128", {160, 1, 1}, 8, 12,
      "as attn_decode_paged_q8kv_d128 with m_q = groups[2] query tokens, causal among themselves (append-then-attend)",
      launch_decode_paged_q8kv_d128},
-    {"attn_decode_paged_q8kv_fused_d128", {128, 1, 1}, 10, 12,
-     "q, k_quants, k_scales, v_quants, v_scales, page_table, part (scratch, as attn_decode_paged_q8kv_d128), tickets u32[KV] (zeroed once; "
-     "the kernel leaves it zero), out f32[m_q*H x128], step | push {n_splits, scale, page} | grid [KV, n_splits, m_q]; decode and combine in "
-     "one launch: the CTA that finishes a kv head last merges that head's splits in index order (the bits of attn_reduce_f32_d128)",
-     launch_decode_paged_q8kv_fused_d128},
-    {"attn_decode_paged_q8kv_xchg_d128", {128, 1, 1}, 12, 24,
-     "q, k_quants, k_scales, v_quants, v_scales, page_table, part, tickets u32[KV], xbuf, peers u64[world] (as attn_reduce_exchange_d128), "
-     "out f32[m_q*H x128], step | push {n_splits u32, scale f32, page u32, world u32, rank u32, wait_us u32} | grid [KV, n_splits, m_q]; "
-     "sequence-parallel decode in one launch: split-K partials, combine, exchange of the merged rows over NVLink, merge in rank order",
-     launch_decode_paged_q8kv_xchg_d128},
     {"attn_decode_paged_q8kv_scalar_d128", {128, 1, 1}, 8, 12,
      "same bindings, push and grid as attn_decode_paged_q8kv_d128; one-warp-per-key CUDA-core statement of the same math",
      launch_decode_paged_q8kv_scalar_d128},
@@ -150,7 +140,7 @@ const KernelEntry REGISTRY[] = {
      "src f16[n x row_len], scales f16, quants i8, page_table u32, step | push {row_len u32, page u32} | row via page table from step[0]+token",
      launch_kv_append_paged_q8_d128},
     {"attn_reduce_exchange_d128", {64, 1, 1}, 4, 16,
-     "part f32[rows x n_splits x 130], xbuf (this rank's exchange buffer: f32[2][world][rows][130], u32[2][world][rows], u32[rows], zeroed once), "
+     "part f32[rows x n_splits x 130], xbuf (this rank's exchange buffer: lines u32[2][world][rows][65][4] = {value, epoch, value, epoch}, then u32[rows]; zeroed once), "
      "peers u64[world] (every rank's xbuf, rank order), out f32[rows x128] | push {n_splits u32, world u32, rank u32, wait_us u32 (0 = about a second)} | "
      "grid [rows]; merges the local splits, stores the row into every rank's buffer over NVLink, waits (bounded) for all ranks' rows, merges in "
      "rank order.  After SGB_ERR_TIMEOUT the row's epoch is not advanced: re-zero every rank's xbuf under a host barrier before reuse",

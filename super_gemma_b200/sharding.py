@@ -76,9 +76,9 @@ def combine_ranks(gathered: np.ndarray) -> np.ndarray:
 
 # ---- the fused combine + exchange of sequence-parallel decode (attn_reduce_exchange_d128) ------------------
 def exchange_words(world: int, rows: int, hd: int = 128) -> int:
-    """4-byte words of one rank's exchange buffer: data f32[2][world][rows][hd + 2], flags u32[2][world][rows],
-    epoch u32[rows]."""
-    return 2 * world * rows * (hd + 2) + 2 * world * rows + rows
+    """4-byte words of one rank's exchange buffer: lines u32[2][world][rows][(hd + 2) / 2][4] (every 16-byte line is
+    {value, epoch, value, epoch}), then epoch u32[rows]."""
+    return 2 * world * rows * ((hd + 2) // 2) * 4 + rows
 
 
 def alloc_exchange(dist, device, world: int, rank: int, rows: int):

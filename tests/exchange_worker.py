@@ -1,7 +1,7 @@
 """One rank of the multi-GPU test of the sequence-parallel decode exchange (launched by tests/test_gpu_exchange.py
-through torch.distributed.run): attn_reduce_exchange_d128 on synthetic partials, and the one-launch decode
-attn_decode_paged_q8kv_xchg_d128 on a real paged Q8_0 shard per rank, must give, step after step, the bits of
-reduce + NCCL all-gather + rank-ordered combine."""
+through torch.distributed.run): attn_reduce_exchange_d128, on synthetic partials and behind the decode kernel on a
+real paged Q8_0 shard per rank, must give, step after step, the bits of reduce + NCCL all-gather + rank-ordered
+combine."""
 import os
 import sys
 
@@ -60,8 +60,8 @@ def main():
         ok = ok and same and finite
         if not (same and finite):
             print(f"rank {rank} step {step}: fused != nccl path (max abs diff {(out_nccl - out_fused).abs().max().item()})", flush=True)
-    # ---- the whole sequence-parallel decode step in ONE launch (attn_decode_paged_q8kv_xchg_d128) against
-    #      decode + reduce + NCCL all-gather + combine, on a real paged Q8_0 shard per rank ------------------------
+    # ---- the sequence-parallel decode step (decode kernel, then attn_reduce_exchange_d128) against decode + reduce +
+    #      NCCL all-gather + combine, on a real paged Q8_0 shard per rank ------------------------------------------
     import bench
 
     dev = bench.Dev.__new__(bench.Dev)
@@ -76,12 +76,11 @@ def main():
         mine2 = torch.zeros(rows2 * (D + 2), dtype=torch.float32, device=device)
         gath2 = torch.zeros(world * rows2 * (D + 2), dtype=torch.float32, device=device)
         o_nccl, o_x = torch.zeros(rows2 * D, dtype=torch.float32, device=device), torch.zeros(rows2 * D, dtype=torch.float32, device=device)
-        tickets = torch.zeros(KV, dtype=torch.int32, device=device)
         step_t = torch.tensor([0, 0, local_len, 0], dtype=torch.int32, device=device)
         xb2, peers2, keep2 = sharding.alloc_exchange(dist, device, world, rank, rows2)
         torch.cuda.synchronize()
         pools = [wrap(t) for t in (q, kq, ks, vq, vs, tab)]
-        dec, xdec = ctx.load_kernel("attn_verify_paged_q8kv_d128"), ctx.load_kernel("attn_decode_paged_q8kv_xchg_d128")
+        dec = ctx.load_kernel("attn_verify_paged_q8kv_d128")
         for it in range(3):
             ctx.dispatch(dec, B(*pools, wrap(part2), wrap(step_t)), (n_splits2, bench.SCALE, PAGE), [KV, n_splits2, m_q])
             ctx.dispatch(redp, B(wrap(part2), wrap(mine2)), n_splits2, [rows2, 1, 1])
@@ -90,13 +89,12 @@ def main():
                 dist.all_gather_into_tensor(gath2, mine2)
             stream.synchronize()
             ctx.dispatch_blocking(comb, B(wrap(gath2), wrap(o_nccl)), world, [rows2, 1, 1])
-            part2.zero_()
-            ctx.dispatch_blocking(xdec, B(*pools, wrap(part2), wrap(tickets), wrap(xb2), wrap(peers2), wrap(o_x), wrap(step_t)),
-                                  (n_splits2, bench.SCALE, PAGE, world, rank, 0), [KV, n_splits2, m_q])
+            ctx.dispatch(dec, B(*pools, wrap(part2), wrap(step_t)), (n_splits2, bench.SCALE, PAGE), [KV, n_splits2, m_q])
+            ctx.dispatch_blocking(fused, B(wrap(part2), wrap(xb2), wrap(peers2), wrap(o_x)), (n_splits2, world, rank, 0), [rows2, 1, 1])
             same = torch.equal(o_nccl.view(torch.int32), o_x.view(torch.int32)) and bool(torch.isfinite(o_x).all())
-            ok = ok and same and not bool(tickets.any())
+            ok = ok and same
             if not same:
-                print(f"rank {rank} m_q {m_q} it {it}: one-launch decode != nccl path (max abs diff {(o_nccl - o_x).abs().max().item()})", flush=True)
+                print(f"rank {rank} m_q {m_q} it {it}: fused exchange != nccl path (max abs diff {(o_nccl - o_x).abs().max().item()})", flush=True)
             dist.barrier()
 
     flag = torch.tensor([1 if ok else 0], device=device)

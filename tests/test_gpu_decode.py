@@ -101,48 +101,6 @@ class PagedCase:
         return part.read().reshape(rows, n_splits, D + 2), out.read().reshape(self.m_q, self.n_kv * G, D)
 
 
-    def run_fused(self, n_splits, tickets=None, kernel="attn_decode_paged_q8kv_fused_d128", xchg=None):
-        """Decode and combine in one launch; with `xchg` = (xbuf, peers, world, rank) also the exchange between ranks."""
-        rows = self.m_q * self.n_kv * G
-        part = self.ctx.new_buffer(rows * n_splits * (D + 2), np.float32)
-        out = self.ctx.new_buffer(rows * D, np.float32)
-        tickets = tickets if tickets is not None else self.ctx.new_buffer(self.n_kv, np.uint32)
-        if xchg is None:
-            self.ctx.dispatch_blocking(self.ctx.load_kernel(kernel), bind(*self.bufs, part, tickets, out, self.step),
-                                       (n_splits, SCALE, self.page), [self.n_kv, n_splits, self.m_q])
-        else:
-            xbuf, peers, world, rank = xchg
-            self.ctx.dispatch_blocking(self.ctx.load_kernel("attn_decode_paged_q8kv_xchg_d128"),
-                                       bind(*self.bufs, part, tickets, xbuf, peers, out, self.step),
-                                       (n_splits, SCALE, self.page, world, rank, 0), [self.n_kv, n_splits, self.m_q])
-        return out.read().reshape(self.m_q, self.n_kv * G, D), tickets
-
-
-@pytest.mark.parametrize("kv_len,m_q,n_splits,n_kv", [(1, 1, 1, 16), (300, 1, 5, 16), (3, 1, 8, 16), (5000, 1, 74, 16), (32768, 1, 74, 16),
-                                                       (1300, 4, 16, 16), (65540, 4, 74, 16), (3000, 1, 8, 4), (700, 2, 3, 6)])
-def test_decode_with_the_combine_folded_in_gives_the_same_bits(ctx, kv_len, m_q, n_splits, n_kv):
-    """attn_decode_paged_q8kv_fused_d128 = attn_decode_paged_q8kv_d128 + attn_reduce_f32_d128 in one launch: the CTA that
-    finishes a head last merges that head's splits in index order, so the output is the two-kernel path's bit for bit,
-    whoever merges; the ticket words are left zero, so the same buffer serves the next launch."""
-    from super_gemma_b200 import sharding
-
-    c = PagedCase(ctx, 0x5640 + kv_len, kv_len, m_q=m_q, n_kv=n_kv)
-    _, want = c.run(n_splits)
-    got, tickets = c.run_fused(n_splits)
-    assert np.array_equal(got.view(np.uint32), want.view(np.uint32))
-    assert not tickets.read().any()
-    again, _ = c.run_fused(n_splits, tickets)
-    assert np.array_equal(again.view(np.uint32), want.view(np.uint32))
-    # the sequence-parallel form with a world of one rank: same bits again (merging one rank's row changes nothing)
-    rows = m_q * n_kv * G
-    xbuf = ctx.new_buffer(sharding.exchange_words(1, rows), np.float32)
-    peers = ctx.buffer_from_iter(np.array([xbuf.device_ptr], np.uint64))
-    for _ in range(3):  # both slot parities
-        solo, _ = c.run_fused(n_splits, tickets, xchg=(xbuf, peers, 1, 0))
-        assert np.array_equal(solo.view(np.uint32), want.view(np.uint32))
-    assert_close(got, c.want(), what=f"fused decode kv_len={kv_len} m_q={m_q}")
-
-
 @pytest.mark.parametrize("kv_len,n_splits", [(1, 1), (17, 4), (63, 2), (64, 1), (65, 3), (300, 5), (3, 8), (1000, 7), (4096, 16)])
 def test_paged_decode_small_and_ragged(ctx, kv_len, n_splits):
     c = PagedCase(ctx, 0x5603 + kv_len, kv_len, page=64 if kv_len < 1000 else 256)

@@ -142,8 +142,8 @@ def test_absent_rank_is_detected_on_the_host(tmp_path):
 
 def test_exchange_buffer_layout():
     """Words of one rank's exchange buffer for attn_reduce_exchange_d128: two parities of world x rows merged rows
-    of 130 floats, their flags, and one epoch per row."""
+    of 65 lines {value, epoch, value, epoch}, and one epoch per row."""
     from super_gemma_b200 import sharding
 
-    assert sharding.exchange_words(1, 32) == 2 * 32 * 130 + 2 * 32 + 32
-    assert sharding.exchange_words(8, 128) == 2 * 8 * 128 * 130 + 2 * 8 * 128 + 128
+    assert sharding.exchange_words(1, 32) == 2 * 32 * 65 * 4 + 32
+    assert sharding.exchange_words(8, 128) == 2 * 8 * 128 * 65 * 4 + 128
