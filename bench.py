@@ -696,6 +696,9 @@ def main():
     ap.add_argument("--no-extra", action="store_true", help="headline workload only")
     ap.add_argument("--no-cpu", action="store_true", help="skip the CPU baseline leg")
     ap.add_argument("--no-e2e", action="store_true", help="skip the end-to-end (host buffers) leg")
+    ap.add_argument("--decode-only", type=int, default=0, metavar="CTX",
+                    help="run only the decode step over a CTX-token cache (decode kernel + combine, graph-replayed) and print its line; "
+                         "for profiler launch lists")
     ap.add_argument("--probe-mma", action="store_true", help="print SM cycles per tcgen05.mma for the shapes the prefill kernels issue, and exit")
     args = ap.parse_args()
     args.warmup = max(args.warmup, 3) if args.impl == "b200" else args.warmup
@@ -727,6 +730,16 @@ def main():
 
     dev = Dev(local_rank)  # raises without the CUDA library or a B200: there is no fallback
     pk = peaks()
+    if args.decode_only:
+        d = run_decode(dev, rank, world, args.steps, args.warmup, dist, args.decode_only, 1,
+                       dev.ctx.decode_splits_hint(KV, args.decode_only // world), 0x5603, copies=2)
+        if rank == 0:
+            d["hbm_frac_kernel"], d["hbm_frac_step"] = d["kernel_gbs"] / pk["hbm_gbs"], d["gbs"] / pk["hbm_gbs"] / world
+            print(json.dumps({"decode_only": args.decode_only, **d}), flush=True)
+        if dist is not None:
+            dist.barrier()
+            dist.destroy_process_group()
+        return
     with ClockSampler(local_rank) as clocks:
         head = run_prefill(dev, rank, world, args.steps, args.warmup, dist, args.m, args.ctx, False, SEED, e2e=not args.no_e2e)
     clk = clocks.summary()

@@ -102,6 +102,15 @@ int sgb_kernel_describe(const sgb_kernel *k, sgb_kernel_info *out);
 /* push block is raw bytes of exactly push_bytes; groups keeps the reference's grid meaning per  */
 /* kernel (see `signature`).  Work is ordered on the stream, which gives the compute->compute    */
 /* barrier the reference recorder inserts before every dispatch (graph.rs:269-273).              */
+/* One kernel family allocates behind the caller's back: attn_prefill_flash_f16_d128 and         */
+/* attn_prefill_paged_q8kv_flash_d128 cut long key ranges into pieces to fill the last wave of   */
+/* CTAs, and keep the pieces' partial results (rows x pieces x 130 floats; 136 MB for a          */
+/* 4096-token chunk of 32 heads in 2 pieces) in a scratch block that the first dispatch needing  */
+/* it cudaMallocs per (device, stream) and the library keeps until the process exits.  A         */
+/* dispatch made while a graph is being recorded never allocates: with no block from an earlier  */
+/* dispatch it runs the same kernel without cutting (same results within rounding, a few per     */
+/* cent slower), so make one un-recorded dispatch of the shape first if the recorded one should  */
+/* cut.  No other kernel of the registry allocates.                                              */
 typedef struct {
     uint32_t index;
     sgb_buffer *buffer;
