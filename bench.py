@@ -61,7 +61,11 @@ def causal_pairs(m, q0):
 # clocks during the timed region
 # --------------------------------------------------------------------------------------------------
 class ClockSampler:
-    Q = ("index,clocks.sm,clocks.max.sm,power.draw,clocks_event_reasons.active,clocks_event_reasons.hw_slowdown,"
+    """nvidia-smi polled every 20 ms while the headline workload runs.  The summary is taken over the samples that fall
+    inside the device-timed window (host clock, see `timed`): the SM clock a kernel actually ran at differs from the
+    clock of the idle or copy-bound phases around it by hundreds of MHz on a power-capped part."""
+
+    Q = ("timestamp,clocks.sm,clocks.max.sm,power.draw,clocks_event_reasons.active,clocks_event_reasons.hw_slowdown,"
          "clocks_event_reasons.hw_thermal_slowdown,clocks_event_reasons.sw_thermal_slowdown,clocks_event_reasons.sw_power_cap")
 
     def __init__(self, device):
@@ -71,7 +75,7 @@ class ClockSampler:
         try:
             f = tempfile.NamedTemporaryFile("w", suffix=".csv", delete=False)
             self.path = f.name
-            self.proc = subprocess.Popen(["nvidia-smi", f"--query-gpu={self.Q}", "--format=csv,noheader,nounits", "-lms", "100",
+            self.proc = subprocess.Popen(["nvidia-smi", f"--query-gpu={self.Q}", "--format=csv,noheader,nounits", "-lms", "20",
                                           "-i", str(self.device)], stdout=f, stderr=subprocess.DEVNULL)
         except Exception:
             self.proc = None
@@ -86,17 +90,23 @@ class ClockSampler:
             except Exception:
                 self.proc.kill()
 
-    def summary(self):
+    def summary(self, window=None):
+        import datetime
+
         out = {"sm_mhz": None, "sm_max_mhz": None, "reasons": []}
         try:
-            rows = [r.split(",") for r in open(self.path).read().strip().splitlines() if r.strip()]
-            sm = [float(r[1]) for r in rows]
-            out["sm_mhz"] = float(np.median(sm))
+            rows = [[c.strip() for c in r.split(",")] for r in open(self.path).read().strip().splitlines() if r.strip()]
+            stamp = lambda r: datetime.datetime.strptime(r[0], "%Y/%m/%d %H:%M:%S.%f").timestamp()
+            inside = [r for r in rows if window and window[0] - 0.01 <= stamp(r) <= window[1] + 0.01]
+            use = inside if inside else rows
+            out["sm_mhz"] = float(np.median([float(r[1]) for r in use]))
             out["sm_max_mhz"] = float(rows[0][2])
-            out["power_w_max"] = max(float(r[3]) for r in rows)
+            out["power_w_max"] = max(float(r[3]) for r in use)
             names = ["hw_slowdown", "hw_thermal_slowdown", "sw_thermal_slowdown", "sw_power_cap"]
-            out["reasons"] = [n for i, n in enumerate(names) if any("Active" in r[5 + i] and "Not" not in r[5 + i] for r in rows)]
-            out["samples"] = len(rows)
+            out["reasons"] = [n for i, n in enumerate(names) if any("Active" in r[5 + i] and "Not" not in r[5 + i] for r in use)]
+            out["samples"] = len(use)
+            out["window"] = "the device-timed steps" if inside else "the whole headline run (no sample fell inside the timed steps)"
+            out["sm_mhz_whole_run"] = float(np.median([float(r[1]) for r in rows]))
             os.unlink(self.path)
         except Exception:
             pass
@@ -239,12 +249,14 @@ def timed(dev, fn, steps, warmup, dist=None, stamps_per_step=1, graph=False):
         dist.barrier()
     torch.cuda.synchronize()
     before = dev.ctx.launch_count
+    t_host0 = time.time()
     if g is not None:
         dev.ctx.submit(g)
     else:
         run_steps()
     dev.ctx.sync()
     torch.cuda.synchronize()
+    dev.last_timed_window = (t_host0, time.time())
     launches = dev.ctx.launch_count - before
     ns = np.array(timer.read_ns(), dtype=np.float64)
     total_s = (ns[-1] - ns[0]) * 1e-9
@@ -290,10 +302,11 @@ def run_prefill(dev, rank, world, steps, warmup, dist, m, ctx_len, identity, see
         dev.ctx.dispatch(flash, dev.bind(b_q, b_kl, b_vl, b_out, b_step), (SCALE, 0), [n_kv, m, 1])
 
     total_s, deltas, launches = timed(dev, step, steps, warmup, dist, stamps_per_step=2)
+    timed_window = dev.last_timed_window
     flop_total = 4.0 * D * causal_pairs(m, q0) * H
     res = {"ms_per_step": total_s / steps * 1e3, "tflops": flop_total * steps / total_s / 1e12, "launches": launches,
            "flash_ms": float(np.mean(deltas[:, 1])) * 1e-6, "dequant_ms": float(np.mean(deltas[:, 0])) * 1e-6,
-           "flop_per_rank": flop_total / world, "flop_total": flop_total}
+           "flop_per_rank": flop_total / world, "flop_total": flop_total, "timed_window": timed_window}
     if check and rank == 0:
         # run by the caller after the timed and clock-sampled region: it is CPU work
         tokens = sorted({0, 1, 63, 64, m // 2, m - 65, m - 64, m - 1} & set(range(m)))
@@ -742,7 +755,7 @@ def main():
         return
     with ClockSampler(local_rank) as clocks:
         head = run_prefill(dev, rank, world, args.steps, args.warmup, dist, args.m, args.ctx, False, SEED, e2e=not args.no_e2e)
-    clk = clocks.summary()
+    clk = clocks.summary(head.pop("timed_window", None))
     check = head.pop("_check", None)
     parity = check() if check else None
     del check
