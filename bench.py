@@ -691,6 +691,36 @@ def probe_mma(n_mma=4096):
                               "issue_cycles_per_mma": float(np.median(c[:, 1]))}), flush=True)
 
 
+def probe_mma_sustained(seconds=3.0, n_mma=1 << 20):
+    """The same instruction streams run for `seconds` each with the clocks and the power sampled: what the tensor pipe
+    alone sustains under the board's power limit, i.e. the ceiling of any kernel built from these instructions."""
+    import super_gemma_b200 as sg
+
+    ctx = sg.GpuContext(0)
+    k = ctx.load_kernel("diag_mma_cycles")
+    sms = sg.lib().sgb_ctx_sm_count(ctx._h)
+    cases = [(0, 2, "SS M128xN64xK16", 2 * 128 * 64 * 16), (1, 2, "SS M128xN128xK16", 2 * 128 * 128 * 16),
+             (2, 2, "TS M128xN128xK16", 2 * 128 * 128 * 16), (3, 2, "8 x SS N128 then 8 x TS N128", 2 * 128 * 128 * 16),
+             (3, 1, "8 x SS N128 then 8 x TS N128", 2 * 128 * 128 * 16)]
+    for data, (shape, per_sm, name, flop) in [(d, c) for d in (2, 1) for c in cases]:
+        buf = ctx.new_buffer(2 * sms * per_sm, np.uint64)
+        bind = [sg.BufferBinding.buffer(0, buf)]
+        ctx.dispatch_blocking(k, bind, (shape, 4096), [per_sm, data, 1])
+        with ClockSampler(0) as clocks:
+            t0 = time.time()
+            launches = 0
+            while time.time() - t0 < seconds:
+                ctx.dispatch_blocking(k, bind, (shape, n_mma), [per_sm, data, 1])
+                launches += 1
+            t1 = time.time()
+        clk = clocks.summary((t0 + 0.5 * (t1 - t0), t1))  # the second half: the clocks have settled by then
+        c = buf.read().reshape(-1, 2).astype(np.float64) / n_mma
+        print(json.dumps({"shape": name, "operands": "seeded values in (-1, 1)" if data == 2 else "all 1.0", "ctas_per_sm": per_sm,
+                          "seconds": t1 - t0, "launches": launches,
+                          "tflops": launches * n_mma * flop * sms * per_sm / (t1 - t0) / 1e12,
+                          "cycles_per_mma_per_sm": float(np.median(c[:, 0])) / per_sm, "clocks": clk}), flush=True)
+
+
 def workload_config(args, world):
     return {"workload": f"BASELINE config 5a: chunked prefill, {args.m} queries at q0={args.ctx - args.m} over {args.ctx} cached "
                         f"Q8_0 tokens (256-token pages, seeded random page table), 32 q / 16 kv heads, head_dim 128, causal",
@@ -713,6 +743,8 @@ def main():
                     help="run only the decode step over a CTX-token cache (decode kernel + combine, graph-replayed) and print its line; "
                          "for profiler launch lists")
     ap.add_argument("--probe-mma", action="store_true", help="print SM cycles per tcgen05.mma for the shapes the prefill kernels issue, and exit")
+    ap.add_argument("--probe-mma-sustained", type=float, default=0.0, metavar="SECONDS",
+                    help="run each tcgen05.mma stream for SECONDS with clocks and power sampled, print TFLOP/s, and exit")
     args = ap.parse_args()
     args.warmup = max(args.warmup, 3) if args.impl == "b200" else args.warmup
 
@@ -721,6 +753,9 @@ def main():
         return
     if args.probe_mma:
         probe_mma()
+        return
+    if args.probe_mma_sustained:
+        probe_mma_sustained(args.probe_mma_sustained)
         return
 
     import torch

@@ -20,15 +20,24 @@ namespace {
 constexpr uint32_t PROBE_SMEM = 96 * 1024;
 
 template <int SHAPE>
-__global__ void __launch_bounds__(64, 2) mma_probe_kernel(uint32_t n_mma, unsigned long long* __restrict__ cycles, uint32_t* status)
+__global__ void __launch_bounds__(64, 2) mma_probe_kernel(uint32_t n_mma, unsigned long long* __restrict__ cycles, uint32_t* status,
+                                                          uint32_t random_data)
 {
     extern __shared__ __align__(1024) uint8_t smem_raw[];
     __shared__ uint64_t done_bar;
     __shared__ uint32_t tmem_base;
     const int tid = threadIdx.x, warp = tid >> 5;
-    // operands: f16 1.0 everywhere (finite, so the result stays finite whatever n_mma is not an issue: D is overwritten
-    // by the first MMA of every group of eight)
-    for (uint32_t i = tid; i < PROBE_SMEM / 4; i += blockDim.x) reinterpret_cast<uint32_t*>(smem_raw)[i] = 0x3C003C00u;
+    // operands: f16 1.0 everywhere, or seeded values in (-1, 1): constant operands toggle few wires and draw far less power
+    // than real data, so a figure meant to stand for a kernel under the board's power limit needs the second kind.
+    // Finite either way: D is overwritten by the first MMA of every group of eight.
+    auto operand_word = [&](uint32_t i) -> uint32_t {
+        if (!random_data) return 0x3C003C00u;
+        uint32_t x = (i + 0x9E3779B9u * (blockIdx.x + 1)) * 2654435761u;
+        x ^= x >> 15, x *= 0x2C1B3C6Du, x ^= x >> 12;
+        const __half2 h = __floats2half2_rn(((int)(x & 0xffffu) - 32768) * (1.0f / 32768.0f), ((int)(x >> 16) - 32768) * (1.0f / 32768.0f));
+        return *reinterpret_cast<const uint32_t*>(&h);
+    };
+    for (uint32_t i = tid; i < PROBE_SMEM / 4; i += blockDim.x) reinterpret_cast<uint32_t*>(smem_raw)[i] = operand_word(i);
     if (tid == 0) {
         mbar_init(&done_bar, 1);
         mbar_fence_init();
@@ -42,10 +51,10 @@ __global__ void __launch_bounds__(64, 2) mma_probe_kernel(uint32_t n_mma, unsign
     __syncthreads();
     tc_fence_after_sync();
     const uint32_t tmem = tmem_base;
-    if (warp == 0) {  // the A operand of the TS shapes: 64 columns of packed f16 ones
+    if (warp == 0) {  // the A operand of the TS shapes: 64 columns of packed f16 values
         uint32_t ones[32];
 #pragma unroll
-        for (int i = 0; i < 32; i++) ones[i] = 0x3C003C00u;
+        for (int i = 0; i < 32; i++) ones[i] = operand_word(0x40000u + tid * 32 + i);
         tmem_st_32x32b_x32(tmem, ones);
         tmem_st_32x32b_x32(tmem + 32, ones);
         tc_wait_st();
@@ -105,7 +114,8 @@ struct PushProbe {
 }  // namespace
 
 // diag_mma_cycles: cycles u64[2 x CTAs] (per CTA: cycles until all MMAs completed, cycles until all were issued).
-// push {shape u32, n_mma u32 (multiple of 16)}.  grid [ctas_per_sm (1 or 2)]: SMs x ctas_per_sm CTAs are launched.
+// push {shape u32, n_mma u32 (multiple of 16)}.  grid [ctas_per_sm (1 or 2), data (0 or 1 = f16 ones, 2 = seeded values
+// in (-1, 1))]: SMs x ctas_per_sm CTAs are launched.
 int launch_diag_mma_cycles(const LaunchArgs& a)
 {
     const PushProbe p = *(const PushProbe*)a.push;
@@ -114,12 +124,13 @@ int launch_diag_mma_cycles(const LaunchArgs& a)
         return fail_validation(a, "diag_mma_cycles: shape 0..3, n_mma a multiple of 16 up to 2^20, groups[0] = CTAs per SM (1 or 2)");
     const uint32_t ctas = (uint32_t)a.sm_count * per_sm;
     if (int r = need_bytes(a, 0, (size_t)ctas * 16, "cycles")) return r;
-    typedef void (*ProbeKernel)(uint32_t, unsigned long long*, uint32_t*);
+    if (a.groups[1] > 2) return fail_validation(a, "diag_mma_cycles: groups[1] = operand data, 0 or 1 (ones) or 2 (seeded values)");
+    typedef void (*ProbeKernel)(uint32_t, unsigned long long*, uint32_t*, uint32_t);
     const ProbeKernel kern = p.shape == 0 ? mma_probe_kernel<0> : p.shape == 1 ? mma_probe_kernel<1> : p.shape == 2 ? mma_probe_kernel<2> : mma_probe_kernel<3>;
     if (int r = check_cuda(a, cudaFuncSetAttribute((const void*)kern, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)PROBE_SMEM),
                            "cudaFuncSetAttribute(mma_probe)"))
         return r;
-    kern<<<ctas, 64, PROBE_SMEM, a.stream>>>(p.n_mma, (unsigned long long*)a.b[0].ptr, a.status);
+    kern<<<ctas, 64, PROBE_SMEM, a.stream>>>(p.n_mma, (unsigned long long*)a.b[0].ptr, a.status, a.groups[1] == 2 ? 1u : 0u);
     ++*a.launches;
     return check_cuda(a, cudaGetLastError(), "diag_mma_cycles");
 }
