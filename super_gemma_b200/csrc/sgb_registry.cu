@@ -170,7 +170,7 @@ const KernelEntry REGISTRY[] = {
     {"diag_mma_cycles", {64, 1, 1}, 1, 8,
      "cycles u64[2 x SMs x groups[0]] (per CTA: cycles until n_mma back-to-back tcgen05.mma completed, cycles until they were issued) | "
      "push {shape u32 (0: SS M128xN64xK16, 1: SS M128xN128xK16, 2: TS M128xN128xK16, 3: 8 of shape 1 then 8 of shape 2, repeated), "
-     "n_mma u32} | grid [CTAs per SM: 1 or 2]; not part of the attention path",
+     "n_mma u32} | grid [CTAs per SM: 1 or 2, operand data: 0 or 1 = f16 ones, 2 = seeded values in (-1, 1)]; not part of the attention path",
      launch_diag_mma_cycles},
 };
 
