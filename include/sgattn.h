@@ -124,7 +124,7 @@ int sgb_dispatch_blocking(sgb_ctx *ctx, const sgb_kernel *k, const sgb_binding *
 uint64_t sgb_launch_count(const sgb_ctx *ctx);
 /* A split count for attn_decode_paged_q8kv_d128 / attn_verify_paged_q8kv_d128 that fills every SM of this
  * device evenly (the reference keeps n_splits as a policy constant, SPLITS_GLOBAL = 32, crates/sg-model/src/graph.rs:37;
- * any value stays valid, this one measured 5-12 % faster than 64 on 148 SMs).  At least 256 tokens per split.
+ * any value stays valid, this one measured 5-12 % faster than 64 on 148 SMs).  At least 512 tokens per split.
  * (sgb_decode_paged_q8kv_d128_noalloc caps m_q * q_heads * n_splits at 2048: 64 splits for 32 q heads.) */
 uint32_t sgb_decode_paged_splits_hint(const sgb_ctx *ctx, uint32_t n_kv_heads, uint32_t kv_len);
 

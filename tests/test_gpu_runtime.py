@@ -112,5 +112,5 @@ def test_decode_splits_hint_fills_the_sms():
     sms = sg.lib().sgb_ctx_sm_count(ctx._h)
     n = ctx.decode_splits_hint(16, 1 << 20)
     assert n == sms * 16 // 32 and (16 * n * 2) % 4 == 0  # two warps per (kv head, split), 16 warps per SM
-    assert ctx.decode_splits_hint(16, 2048) == 8           # at least 256 tokens per split
+    assert ctx.decode_splits_hint(16, 2048) == 4           # at least 512 tokens per split
     assert ctx.decode_splits_hint(16, 10) == 1
