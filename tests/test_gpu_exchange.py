@@ -65,6 +65,44 @@ def test_two_ranks_match_the_nccl_path():
     assert r.returncode == 0 and "exchange worker: OK" in r.stdout, r.stdout[-2000:] + r.stderr[-2000:]
 
 
+@pytest.mark.parametrize("world", [4, 8])
+def test_many_ranks_on_one_gpu_the_last_rank_finds_every_row(world):
+    """Slot addressing for 4 and 8 ranks without 4 or 8 GPUs: every rank's exchange buffer lives on this GPU and the
+    ranks are launched one after the other.  A rank stores its rows into all buffers before it waits, so ranks
+    0 .. world-2 give up after their (20 us) bounded wait -- the ranks after them have not run yet -- and report a
+    timeout, and the last rank finds every row in place and must produce exactly what the NCCL form produces:
+    attn_reduce_partial_d128 per rank, the partials laid out in rank order, attn_combine_ranks_d128.  Nothing here
+    waits for a launch that is not running: every wait runs out by itself."""
+    import super_gemma_b200 as sg
+    from super_gemma_b200 import sharding
+
+    ctx = sg.GpuContext(0)
+    rows, n_splits = 32, 5
+    bufs = [ctx.new_buffer(sharding.exchange_words(world, rows), np.float32) for _ in range(world)]
+    peers = ctx.buffer_from_iter(np.array([b.device_ptr for b in bufs], np.uint64))
+    rng = np.random.default_rng(40 + world)
+    parts = []
+    for r in range(world):
+        part = rng.standard_normal((rows, n_splits, D + 2)).astype(np.float32)
+        part[:, :, D] += 3.0 * r  # the ranks' maxima differ, so the order of the merge shows in the bits
+        part[:, :, D + 1] = np.abs(part[:, :, D + 1]) + 0.25
+        parts.append(ctx.buffer_from_iter(part.reshape(-1)))
+    redp, comb, fused = (ctx.load_kernel(n) for n in ("attn_reduce_partial_d128", "attn_combine_ranks_d128", "attn_reduce_exchange_d128"))
+    gathered = ctx.new_buffer(world * rows * (D + 2), np.float32)
+    one = ctx.new_buffer(rows * (D + 2), np.float32)
+    for r in range(world):
+        ctx.dispatch_blocking(redp, bind(parts[r], one), n_splits, [rows, 1, 1])
+        gathered.write(one.read(), r * rows * (D + 2))
+    want = ctx.new_buffer(rows * D, np.float32)
+    ctx.dispatch_blocking(comb, bind(gathered, want), world, [rows, 1, 1])
+    out = ctx.new_buffer(rows * D, np.float32)
+    for r in range(world - 1):
+        with pytest.raises(sg.Timeout):
+            ctx.dispatch_blocking(fused, bind(parts[r], bufs[r], peers, out), (n_splits, world, r, 20), [rows, 1, 1])
+    ctx.dispatch_blocking(fused, bind(parts[world - 1], bufs[world - 1], peers, out), (n_splits, world, world - 1, 0), [rows, 1, 1])
+    assert np.array_equal(out.read().view(np.uint32), want.read().view(np.uint32))
+
+
 def test_absent_peer_ends_in_a_timeout_status_not_a_hang():
     """The wait for a peer's row is bounded (the push block's wait_us, here 50 ms; about a second by default): with a second rank that never stores its row the kernel
     gives up, reports DEV_ERR_TIMEOUT through the status word, writes NaN (never stale data), and the context stays
