@@ -188,6 +188,22 @@ def test_flash_key_range_cut_into_pieces(ctx, monkeypatch, pieces, m, q0, window
     assert np.array_equal(got.view(np.uint32), again.view(np.uint32))
 
 
+@pytest.mark.parametrize("group", [1, 2, 4, 8, 16])
+def test_flash_launch_order_does_not_change_the_bits(ctx, monkeypatch, group):
+    """The launcher interleaves the query tiles of `group` kv heads in launch order (it picks the group from the K/V
+    size; forced here): which CTA computes which (kv head, query tile) changes, the result does not, bit for bit."""
+    m, q0 = 200, 300
+    q16, k16, v16, bufs = _linear_case(ctx, 0x5631, m, q0)
+    want = O.attention_f64(q16.astype(np.float32), k16.astype(np.float32), v16.astype(np.float32), m, q0, H, KV, D, SCALE)
+    monkeypatch.setenv("SGB_FLASH_PIECES", "2")
+    monkeypatch.setenv("SGB_FLASH_HEAD_GROUP", "1")
+    base = _run_linear(ctx, "attn_prefill_flash_f16_d128", bufs, m, q0, KV, (SCALE, 0))
+    assert_close(base, want, what="flash, heads one after the other")
+    monkeypatch.setenv("SGB_FLASH_HEAD_GROUP", str(group))
+    got = _run_linear(ctx, "attn_prefill_flash_f16_d128", bufs, m, q0, KV, (SCALE, 0))
+    assert np.array_equal(got.view(np.uint32), base.view(np.uint32))
+
+
 # ---- head_dim 128: ring history + chunk ------------------------------------------------------------------
 @pytest.mark.parametrize("q0,m", [(0, 64), (100, 64), (1000, 64), (1531, 64), (1531, 200), (66000, 4)])
 def test_sliding_ring_d128(ctx, q0, m):
